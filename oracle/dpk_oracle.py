@@ -1,0 +1,304 @@
+"""CPU oracle for the routed dynamic-width operators.  TEST INFRASTRUCTURE ONLY.
+
+This module restates, in plain fp32 PyTorch on the CPU, what the reference's
+PyTorch backend computes for the four operator families and for the routing
+layout that precedes them.  It exists so that the CUDA kernels can be checked
+against an independent statement of the semantics.  Nothing in the shipped
+package imports it; only the tests, the smoke entry and the CPU-baseline leg of
+the benchmark do.
+
+Parity status: PINNED.  ``tests/golden/*.npz`` were produced by running the
+reference's own ``run_kernel(..., backend="torch")`` on seeded inputs (see
+``tests/golden/make_golden.py``); ``tests/test_oracle_golden.py`` checks every
+function below against them, including the reference's hand-written
+known-answer cases (``DynamicPruningKernels/tests/test_references.py:11-84``).
+
+Each function cites the reference lines it follows.  The formulations are
+deliberately different from the reference's (explicit per-group loops and an
+explicit softmax instead of dense-then-mask and SDPA) so that an error in one
+is unlikely to be mirrored in the other.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+__all__ = [
+    "as_group_mask",
+    "topk_route_mask",
+    "route_compact",
+    "gemm_mn",
+    "gemm_k",
+    "ffn_swiglu",
+    "attention",
+    "attention_prefill",
+    "attention_decode",
+    "dense_then_mask_ffn",
+    "rel_err",
+]
+
+
+# ----------------------------------------------------------------------------
+# routing
+# ----------------------------------------------------------------------------
+
+def as_group_mask(mask: torch.Tensor, batch: int, tokens: int) -> torch.Tensor:
+    """``[B,T]`` or ``[B,T,NG]`` of any dtype -> bool ``[B,T,NG]``.
+
+    Follows ``DynamicPruningKernels/python/references.py:11-19``: a 2-D mask is
+    one group spanning the whole width (whole-token skip).
+    """
+    if mask.dim() == 2:
+        mask = mask[..., None]
+    if mask.dim() != 3 or tuple(mask.shape[:2]) != (batch, tokens):
+        raise ValueError("Mask must have shape [batch, tokens] or [batch, tokens, groups]")
+    return mask != 0
+
+
+def topk_route_mask(logits: torch.Tensor, keep: int) -> torch.Tensor:
+    """Benchmark-defined router: each token keeps its ``keep`` largest logits.
+
+    The reference ships no top-k router (its kernels take a ready Boolean
+    mask, ``DynamicPruningKernels/README.md:35``; WIDE's evaluation routing is
+    a 2-way argmax, ``WIDE/wrapper/base_layer.py:204-207``).  Ties are broken
+    towards the lower group index, which is what the CUDA router does.
+    """
+    if not 0 <= keep <= logits.shape[-1]:
+        raise ValueError("keep out of range")
+    l32 = logits.to(torch.float32)
+    order = torch.sort(l32, dim=-1, descending=True, stable=True).indices
+    mask = torch.zeros(l32.shape, dtype=torch.bool)
+    mask.scatter_(-1, order[..., :keep], True)
+    return mask
+
+
+def route_compact(mask2d: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Routing layout for a flattened ``[M,NG]`` mask.
+
+    Returns ``(sorted_mask bool[M,NG], sorted_indices int64[M,NG], counts
+    int32[NG])``: per group column the active rows first, in ascending row
+    order, then the inactive rows in ascending order.  The reference builds
+    the same layout with ``torch.sort(mask, dim=0, descending=True,
+    stable=False)`` (``python/gemm_mn/jit.py:410-415``); its kernels rely only
+    on "all True rows precede all False rows" (``include/gemm_mn/v1/sm12x.cuh:
+    272-311``).  The order among equal keys is unspecified there; this build
+    fixes the stable order, so this oracle is a plain loop.
+    """
+    m = (mask2d != 0)
+    M, NG = m.shape
+    smask = torch.zeros((M, NG), dtype=torch.bool)
+    sidx = torch.zeros((M, NG), dtype=torch.int64)
+    counts = torch.zeros((NG,), dtype=torch.int32)
+    rows = torch.arange(M, dtype=torch.int64)
+    for g in range(NG):
+        col = m[:, g]
+        act = rows[col]
+        ina = rows[~col]
+        c = act.numel()
+        counts[g] = c
+        smask[:c, g] = True
+        sidx[:c, g] = act
+        sidx[c:, g] = ina
+    return smask, sidx, counts
+
+
+# ----------------------------------------------------------------------------
+# routed GEMMs
+# ----------------------------------------------------------------------------
+
+def _act(x: torch.Tensor, activation: str) -> torch.Tensor:
+    if activation == "identity":
+        return x
+    if activation == "relu":
+        return torch.clamp_min(x, 0)
+    if activation == "silu":
+        return x / (1.0 + torch.exp(-x))
+    raise ValueError(f"Unsupported activation: {activation}")
+
+
+def gemm_mn(A: torch.Tensor, W: torch.Tensor, mask: torch.Tensor,
+            activation: str = "identity") -> torch.Tensor:
+    """Output-width routed projection.
+
+    ``D[b,t, g*G:(g+1)*G] = act(A[b,t,:] @ W[g*G:(g+1)*G,:]^T)`` where group
+    ``g`` is active for token ``(b,t)``, zero elsewhere
+    (``python/references.py:29-61``; act(0)=0 for all three activations so
+    masking before or after the activation is the same).
+    """
+    if A.dim() != 3 or W.dim() != 2:
+        raise ValueError("A must be [B, T, K] and W must be [N, K]")
+    B, T, K = A.shape
+    N = W.shape[0]
+    gm = as_group_mask(mask, B, T)
+    NG = gm.shape[-1]
+    if N % NG:
+        raise ValueError(f"Output width {N} must be divisible by groups {NG}")
+    G = N // NG
+    a = A.reshape(B * T, K).to(torch.float32)
+    w = W.to(torch.float32)
+    gm2 = gm.reshape(B * T, NG)
+    out = torch.zeros((B * T, N), dtype=torch.float32)
+    for g in range(NG):
+        rows = torch.nonzero(gm2[:, g]).flatten()
+        if rows.numel() == 0:
+            continue
+        out[rows, g * G:(g + 1) * G] = _act(a[rows] @ w[g * G:(g + 1) * G].T, activation)
+    return out.reshape(B, T, N)
+
+
+def gemm_k(A: torch.Tensor, W: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    """Reduction-width routed projection.
+
+    ``D[b,t,:] = sum over active g of A[b,t, g*G:(g+1)*G] @ W[:, g*G:(g+1)*G]^T``
+    (``python/references.py:64-86``).  Whatever the caller left in the
+    inactive column blocks of ``A`` does not contribute.
+    """
+    if A.dim() != 3 or W.dim() != 2:
+        raise ValueError("A must be [B, T, K] and W must be [N, K]")
+    B, T, K = A.shape
+    N = W.shape[0]
+    gm = as_group_mask(mask, B, T)
+    NG = gm.shape[-1]
+    if K % NG:
+        raise ValueError(f"Input width {K} must be divisible by groups {NG}")
+    G = K // NG
+    a = A.reshape(B * T, K).to(torch.float32)
+    w = W.to(torch.float32)
+    gm2 = gm.reshape(B * T, NG)
+    out = torch.zeros((B * T, N), dtype=torch.float32)
+    for g in range(NG):
+        rows = torch.nonzero(gm2[:, g]).flatten()
+        if rows.numel() == 0:
+            continue
+        out[rows] += a[rows, g * G:(g + 1) * G] @ w[:, g * G:(g + 1) * G].T
+    return out.reshape(B, T, N)
+
+
+def ffn_swiglu(x: torch.Tensor, Wg: torch.Tensor, Wu: torch.Tensor, Wd: torch.Tensor,
+               mask: torch.Tensor, round_intermediate: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Dynamic-width SwiGLU FFN: ``down(mask * silu(gate(x)) * up(x))``.
+
+    Composition used by the reference's callers:
+    ``gemm_k(gemm_mn(x,Wg,silu) * gemm_mn(x,Wu), Wd)``
+    (``PruningInferSim/ops/mlp/m_pruning.py:76-105``), equal to WIDE's
+    ``down_proj(apply_mask(swiglu(gate_proj(x), up_proj(x))))``
+    (``WIDE/wrapper/attn_group_ffn_block.py:33-38``).  ``round_intermediate``
+    optionally rounds the intermediate to the GPU's storage dtype so that the
+    comparison isolates kernel error from the unavoidable bf16 hand-off.
+    """
+    h = gemm_mn(x, Wg, mask, "silu") * gemm_mn(x, Wu, mask, "identity")
+    if round_intermediate is not None:
+        h = h.to(round_intermediate).to(torch.float32)
+    return gemm_k(h, Wd, mask)
+
+
+def dense_then_mask_ffn(x, Wg, Wu, Wd, mask):
+    """The reference CPU path's cost model: dense GEMMs, then mask.
+
+    ``python/references.py:50-53, 83-85`` compute the full-width product and
+    ``masked_fill`` afterwards, so on the CPU the routed FFN costs as much as
+    the dense one.  Used only as the timed CPU baseline.
+    """
+    B, T, _ = x.shape
+    gm = as_group_mask(mask, B, T)
+    NG = gm.shape[-1]
+    x32, wg, wu, wd = (t.to(torch.float32) for t in (x, Wg, Wu, Wd))
+    gate = torch.nn.functional.silu(x32 @ wg.T)
+    up = x32 @ wu.T
+    h = (gate * up).reshape(B, T, NG, -1)
+    h = h.masked_fill(~gm[..., None], 0).reshape(B, T, -1)
+    return h @ wd.T
+
+
+# ----------------------------------------------------------------------------
+# routed attention
+# ----------------------------------------------------------------------------
+
+def attention(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, mask: torch.Tensor,
+              scale: Optional[float] = None, leftpad: Optional[torch.Tensor] = None,
+              is_causal: bool = False, q_chunk: int = 1024) -> torch.Tensor:
+    """Query-head-group routed attention (``python/references.py:89-149``).
+
+    ``Q,O: [B,Tq,Hq,D]``; ``K,V: [B,Tk,Hk,D]``; ``mask: [B,Tq,NG]``.  Group
+    ``g`` is the ``Hq/NG`` consecutive query heads ``[g*Hq/NG, (g+1)*Hq/NG)``;
+    query head ``h`` reads KV head ``h // (Hq/Hk)``.  Inactive (token, group)
+    pairs give zero output rows.  Causal alignment follows the reference's
+    PyTorch path exactly: top-left (``k <= q``, SDPA's ``is_causal``) when no
+    ``Leftpad`` is given, bottom-right (``k <= q + Tk - Tq``) when one is
+    (``references.py:123-139``); the two agree when ``Tq == Tk``.  Keys
+    ``k < leftpad[b]`` are excluded.
+    """
+    if Q.dim() != 4 or K.dim() != 4 or V.dim() != 4:
+        raise ValueError("Q, K, and V must have shape [B, T, H, D]")
+    if K.shape != V.shape:
+        raise ValueError("K and V must have matching shapes")
+    B, Tq, Hq, D = Q.shape
+    Tk, Hk = K.shape[1], K.shape[2]
+    gm = as_group_mask(mask, B, Tq)
+    NG = gm.shape[-1]
+    if Hq % NG:
+        raise ValueError(f"Query heads {Hq} must be divisible by groups {NG}")
+    if Hq % Hk:
+        raise ValueError("Hq must be a multiple of Hk")
+    hpg = Hq // NG
+    rep = Hq // Hk
+    sc = float(scale) if scale is not None else 1.0 / math.sqrt(D)
+    out = torch.zeros((B, Tq, Hq, D), dtype=torch.float32)
+    kpos = torch.arange(Tk)
+    causal_shift = (Tk - Tq) if leftpad is not None else 0
+    for b in range(B):
+        lp = int(leftpad[b]) if leftpad is not None else 0
+        for h in range(Hq):
+            g = h // hpg
+            rows = torch.nonzero(gm[b, :, g]).flatten()
+            if rows.numel() == 0:
+                continue
+            kh = K[b, :, h // rep, :].to(torch.float32)
+            vh = V[b, :, h // rep, :].to(torch.float32)
+            for c0 in range(0, rows.numel(), q_chunk):
+                r = rows[c0:c0 + q_chunk]
+                q = Q[b, r, h, :].to(torch.float32)
+                s = (q @ kh.T) * sc
+                allow = (kpos[None, :] >= lp)
+                if is_causal:
+                    allow = allow & (kpos[None, :] <= (r[:, None] + causal_shift))
+                s = s.masked_fill(~allow, float("-inf"))
+                mx = s.max(dim=-1, keepdim=True).values
+                mx = torch.where(torch.isinf(mx), torch.zeros_like(mx), mx)
+                p = torch.exp(s - mx)
+                den = p.sum(dim=-1, keepdim=True)
+                # a row with every key excluded (query before its batch's leftpad
+                # under causal masking) comes out as zeros from the reference's
+                # SDPA call; keep that
+                o = torch.where(den > 0, (p @ vh) / den, torch.zeros(()))
+                out[b, r, h, :] = o
+    return out
+
+
+def attention_prefill(Q, K, V, mask, **kw):
+    """``python/references.py:152-163``: causal unless told otherwise."""
+    kw.setdefault("is_causal", True)
+    return attention(Q, K, V, mask, **kw)
+
+
+def attention_decode(Q, K, V, mask, **kw):
+    """``python/references.py:166-175``: one query token, non-causal."""
+    kw.setdefault("is_causal", False)
+    return attention(Q, K, V, mask, **kw)
+
+
+# ----------------------------------------------------------------------------
+# error metric
+# ----------------------------------------------------------------------------
+
+def rel_err(actual: torch.Tensor, expected: torch.Tensor) -> float:
+    """max|actual-expected| / rms(expected): the tolerance is stated on this."""
+    e = expected.to(torch.float32)
+    a = actual.to(torch.float32).reshape(e.shape)
+    rms = float(torch.sqrt(torch.mean(e * e)))
+    if rms == 0.0:
+        return float((a - e).abs().max())
+    return float((a - e).abs().max()) / rms

@@ -1,0 +1,92 @@
+"""The CPU oracle against fixtures produced by the reference itself (CPU only)."""
+
+import numpy as np
+import torch
+
+import golden_io
+from oracle import dpk_oracle as O
+from oracle import route_oracle as RO
+
+TIGHT = dict(atol=2e-5, rtol=2e-5)
+
+
+def test_reference_known_answer_cases():
+    z = golden_io.load("ref_known_answers")
+    torch.testing.assert_close(O.gemm_mn(z["x"], z["out_w"], z["mask"]), z["gemm_mn"], **TIGHT)
+    torch.testing.assert_close(O.gemm_k(z["inter"], z["down_w"], z["mask"]), z["gemm_k"], **TIGHT)
+    torch.testing.assert_close(O.gemm_mn(z["x"], z["out_w"], z["tok_mask"]), z["gemm_mn_token"],
+                               **TIGHT)
+    out = O.attention_decode(z["q"], z["k"], z["v"], torch.ones(1, 1, 2, dtype=torch.bool),
+                             leftpad=z["leftpad"])
+    torch.testing.assert_close(out, z["decode_leftpad"], **TIGHT)
+
+
+def test_ffn_small():
+    z = golden_io.load("ffn_small")
+    m = z["mask"]
+    torch.testing.assert_close(O.gemm_mn(z["x"], z["wg"], m, "silu"), z["gate"], **TIGHT)
+    torch.testing.assert_close(O.gemm_mn(z["x"], z["wu"], m), z["up"], **TIGHT)
+    torch.testing.assert_close(O.gemm_mn(z["x"], z["wu"], m, "relu"), z["relu"], **TIGHT)
+    torch.testing.assert_close(O.gemm_k(z["hmid"], z["wd"], m), z["down"], **TIGHT)
+    torch.testing.assert_close(O.gemm_k(z["dense_a"], z["wd"], m), z["down_dense_a"], **TIGHT)
+    torch.testing.assert_close(
+        O.ffn_swiglu(z["x"], z["wg"], z["wu"], z["wd"], m, round_intermediate=torch.bfloat16),
+        z["down"], **TIGHT)
+    torch.testing.assert_close(O.dense_then_mask_ffn(z["x"], z["wg"], z["wu"], z["wd"], m),
+                               O.ffn_swiglu(z["x"], z["wg"], z["wu"], z["wd"], m),
+                               atol=1e-4, rtol=1e-4)
+    # the top-k router reproduces the mask the fixture was built with
+    assert torch.equal(O.topk_route_mask(z["logits"], 2), m)
+
+
+def test_routing_layout_python_and_c():
+    z = golden_io.load("routing")
+    smask, sidx, counts = O.route_compact(z["mask"])
+    assert torch.equal(smask, z["sorted_mask"])
+    assert torch.equal(sidx, z["sorted_indices"])
+    assert torch.equal(counts, z["counts"])
+    cs, ci, cc = RO.route_compact(z["mask"].numpy())
+    assert np.array_equal(cs, z["sorted_mask"].numpy())
+    assert np.array_equal(ci, z["sorted_indices"].numpy())
+    assert np.array_equal(cc, z["counts"].numpy())
+    # top-k: same active set as torch.topk
+    want = torch.zeros_like(z["mask"])
+    want.scatter_(-1, z["topk5"], True)
+    assert torch.equal(O.topk_route_mask(z["logits"], 5), want)
+    assert np.array_equal(RO.topk_mask(z["logits"].numpy(), 5), want.numpy())
+
+
+def test_row_bits_c():
+    z = golden_io.load("routing")
+    m = z["mask"].numpy()
+    rb, wb = RO.row_bits(m, 128)
+    M, NG = m.shape
+    for r in (0, 1, 127, 128, 332):
+        for g in range(NG):
+            assert ((rb[r, g // 32] >> (g % 32)) & 1) == int(m[r, g])
+    for w in range((M + 127) // 128):
+        want = np.bitwise_or.reduce(rb[w * 128:(w + 1) * 128], axis=0)
+        assert np.array_equal(wb[w], want)
+
+
+def test_prefill_attention():
+    z = golden_io.load("attn_prefill_small")
+    q, k, v = z["q"], z["k"], z["v"]
+    torch.testing.assert_close(O.attention_prefill(q, k, v, z["mask2"]), z["causal_ng2"], **TIGHT)
+    torch.testing.assert_close(O.attention_prefill(q, k, v, z["mask8"]), z["causal_ng8"], **TIGHT)
+    torch.testing.assert_close(O.attention_prefill(q, k, v, z["mask2"], is_causal=False),
+                               z["full_ng2"], **TIGHT)
+    torch.testing.assert_close(
+        O.attention_prefill(q, k, v, z["mask2"], leftpad=z["leftpad"]), z["causal_ng2_leftpad"],
+        equal_nan=True, **TIGHT)
+    z = golden_io.load("attn_prefill_d128")
+    torch.testing.assert_close(O.attention_prefill(z["q"], z["k"], z["v"], z["mask2"]),
+                               z["causal_ng2"], **TIGHT)
+
+
+def test_decode_attention():
+    z = golden_io.load("attn_decode_small")
+    q, k, v = z["q"], z["k"], z["v"]
+    torch.testing.assert_close(O.attention_decode(q, k, v, z["mask8"]), z["out_ng8"], **TIGHT)
+    torch.testing.assert_close(O.attention_decode(q, k, v, z["mask16"], leftpad=z["leftpad"]),
+                               z["out_ng16_leftpad"], **TIGHT)
