@@ -1,0 +1,206 @@
+/*
+ * dpk_b200 -- C ABI of the B200 (sm_100a) routed dynamic-width operators.
+ *
+ * This is the native boundary a host binding calls in place of the reference's
+ * TVM-FFI `Host::run(TensorView...)` functions.  Every entry point takes raw
+ * device pointers, sizes, element strides and a CUDA stream, launches on that
+ * stream without synchronising, allocates nothing and keeps no state besides
+ * cached device properties.  All return 0 on success or one of the DPK_ERR_*
+ * codes; dpk_last_error() then holds a message (thread local).
+ *
+ * Conventions
+ *   - "half" tensors are fp16 or bf16 as selected by `dtype` (DPK_F16 / DPK_BF16),
+ *     row-major, innermost dimension contiguous, 16-byte aligned rows.
+ *   - M = B*T flattened tokens, NG = routed groups, G = group width.
+ *   - masks are one byte per element, non-zero = active (a torch.bool tensor).
+ *   - `stream` is a cudaStream_t passed as void*.
+ *   - workspaces are caller-owned device buffers; their sizes come from the
+ *     dpk_*_workspace_bytes() helpers.
+ */
+#ifndef DPK_B200_H_
+#define DPK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DPK_OK 0
+#define DPK_ERR_INVALID 1     /* bad argument: shape, stride, alignment, dtype  */
+#define DPK_ERR_CUDA 2        /* a CUDA runtime / driver call failed              */
+#define DPK_ERR_UNSUPPORTED 3 /* valid request this build has no kernel for       */
+#define DPK_ERR_DEVICE 4      /* a kernel reported a problem in its status word   */
+
+#define DPK_F16 0
+#define DPK_BF16 1
+
+#define DPK_ACT_IDENTITY 0
+#define DPK_ACT_RELU 1
+#define DPK_ACT_SILU 2
+
+/* Library version (major*100 + minor). */
+int dpk_version(void);
+
+/* Message of the last failing call made by this thread ("" if none). */
+const char* dpk_last_error(void);
+
+/*
+ * Reads (and clears) the status word kernels write when a bounded wait ran out or a
+ * routing index was out of range.  Synchronises `stream`.  *status == 0 means fine.
+ * The reference's device code has no counterpart: its waits are unbounded
+ * (DynamicPruningKernels/include/attention_prefill/v3/sm12x_causal.cuh:401,535).
+ */
+int dpk_device_status(int* status, void* stream);
+
+/* ------------------------------------------------------------------ routing ---- */
+
+/*
+ * Per-token top-k over fp32 router logits [M,NG] -> byte mask [M,NG]; ties go to the
+ * lower group index.  The reference ships no top-k router (its kernels consume a
+ * ready Boolean mask, DynamicPruningKernels/README.md:35; WIDE's evaluation routing is
+ * a 2-way argmax, WIDE/wrapper/base_layer.py:204-207); this is the benchmark's way of
+ * producing a mask with an exact keep count.
+ */
+int dpk_topk_mask(const float* logits, int64_t M, int NG, int keep, uint8_t* mask, void* stream);
+
+/* Bytes of scratch dpk_route_compact needs for an [M,NG] mask. */
+size_t dpk_route_workspace_bytes(int batches, int64_t M, int NG);
+
+/*
+ * Routing layout.  Replaces the reference hosts'
+ *   torch.sort(Mask.flatten(0,1), dim=0, descending=True, stable=False)
+ * (DynamicPruningKernels/python/gemm_mn/jit.py:410-415, gemm_k/jit.py:396-401) with
+ * batches = 1, M = B*T, and the per-batch sort of prefill attention
+ *   torch.sort(Mask, dim=1, descending=True, stable=False)
+ * (attention_prefill/jit.py:259-263) with batches = B, M = Tq (indices then count
+ * from 0 inside each batch, as the reference's do).
+ *   mask            [batches,M,NG] bytes
+ *   sorted_mask     [batches,M,NG] bytes: row r of column g is 1 iff r < counts[b,g]
+ *   sorted_indices  [batches,M,NG] int64: column g lists the active rows ascending,
+ *                   then the inactive rows ascending (the stable order)
+ *   counts          [batches,NG] int32 active rows per group
+ */
+int dpk_route_compact(const uint8_t* mask, int batches, int64_t M, int NG, uint8_t* sorted_mask,
+                      int64_t* sorted_indices, int32_t* counts, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
+/*
+ * counts[b,g] = number of non-zero entries of column g of sorted_mask [batches,M,NG].  Used
+ * when the caller passes `sorted_mask` / `sorted_indices` from an earlier call
+ * (metadata reuse, DynamicPruningKernels/tests/test_gpu_smoke.py:203-292).
+ */
+int dpk_route_counts(const uint8_t* sorted_mask, int batches, int64_t M, int NG, int32_t* counts,
+                     void* stream);
+
+/*
+ * Packed routing bits for the reduction-width GEMM: row_bits [M, ceil(NG/32)] uint32
+ * (bit g%32 of word g/32 = mask[r,g] != 0) and win_bits [ceil(M/128), ceil(NG/32)]
+ * (OR over each 128-row window).  Plays the role of the reference kernel's per-tile
+ * skip metadata (DynamicPruningKernels/include/gemm_k/v1/sm12x.cuh:258-358, 525).
+ */
+int dpk_mask_pack(const uint8_t* mask, int64_t M, int NG, uint32_t* row_bits, uint32_t* win_bits,
+                  void* stream);
+
+/* ------------------------------------------------------------ routed GEMMs ---- */
+
+/*
+ * Output-width routed projection (reference: GEMM_MN_V1_Host::run,
+ * DynamicPruningKernels/include/gemm_mn/v1/sm12x.cuh:766-860; host wrapper
+ * python/gemm_mn/jit.py:357-440).
+ *   D[t, g*G + j] = act( sum_k A[t,k] * W[g*G + j, k] )      for active (t,g)
+ * Rows of inactive (t,g) blocks are not written: pass D zero-filled, as the reference
+ * host does (jit.py:381).
+ *   A [M,K] lda, W [N,K] ldw, D [M,N] ldd   (strides in elements)
+ *   W2: optional second weight [N,K] (same ldw).  When non-NULL the kernel computes the
+ *       SwiGLU combination D = silu(A W^T) * (A W2^T) in one pass (`act` ignored);
+ *       this fuses the reference callers' gate GEMM, up GEMM and multiply
+ *       (PruningInferSim/ops/mlp/m_pruning.py:76-105).
+ *   sorted_indices [M,NG] int64 and counts [NG] int32 from dpk_route_compact.
+ * Requirements: K % 8 == 0, G = N/NG a multiple of 16, 16-byte aligned rows.
+ */
+int dpk_gemm_mn(const void* A, int64_t lda, const void* W, const void* W2, int64_t ldw,
+                const int64_t* sorted_indices, const int32_t* counts, void* D, int64_t ldd,
+                int64_t M, int N, int K, int NG, int dtype, int act, void* stream);
+
+/*
+ * Reduction-width routed projection (reference: GEMM_K_V1_Host::run,
+ * DynamicPruningKernels/include/gemm_k/v1/sm12x.cuh:738-832; host wrapper
+ * python/gemm_k/jit.py:345-425).
+ *   D[t, n] = sum over active g, j of A[t, g*G + j] * W[n, g*G + j]
+ * D is overwritten (the behaviour of the reference's PyTorch path,
+ * python/references.py:21-26, 83-86), accumulated in fp32 without atomics.
+ *   A [M,K] lda, W [N,K] ldw, D [M,N] ldd; row_bits / win_bits from dpk_mask_pack.
+ * Requirements: G = K/NG a multiple of 64, N % 8 == 0, 16-byte aligned rows.
+ */
+int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw, const uint32_t* row_bits,
+               const uint32_t* win_bits, void* D, int64_t ldd, int64_t M, int N, int K, int NG,
+               int dtype, void* stream);
+
+/*
+ * Small-batch / odd-shape routed projections on CUDA cores, reading the byte mask
+ * directly (reference: GEMV_MN_V0_Host::run, include/gemv_mn/v0/sm8x.cuh:277-359 and
+ * GEMV_K_V0_Host::run, include/gemv_k/v0/sm8x.cuh:216-295; dispatch rules
+ * python/gemm_mn/jit.py:41,388 and python/gemm_k/jit.py:337-342).  `reduce_k` = 0 is
+ * the gemm_mn semantics (inactive blocks left untouched), 1 the gemm_k semantics.
+ * Requirement: K % 8 == 0.
+ */
+int dpk_gemv_routed(const void* A, int64_t lda, const void* W, int64_t ldw, const uint8_t* mask,
+                    void* D, int64_t ldd, int64_t M, int N, int K, int NG, int dtype, int act,
+                    int reduce_k, void* stream);
+
+/* Bytes of scratch dpk_ffn_swiglu needs (routing layout, packed bits, intermediate). */
+size_t dpk_ffn_workspace_bytes(int64_t M, int H, int I, int NG);
+
+/*
+ * Dynamic-width SwiGLU FFN in one call:
+ *   y = down( mask * silu(gate(x)) * up(x) )
+ * = routing layout + packed bits + fused gate/up GEMM + reduction-width down GEMM.
+ * Replaces the caller-side composition gemm_mn(silu) / gemm_mn / multiply / gemm_k
+ * (PruningInferSim/ops/mlp/m_pruning.py:76-105; WIDE/wrapper/attn_group_ffn_block.py:33-38).
+ *   x [M,H], Wg,Wu [I,H], Wd [H,I], mask [M,NG] bytes, y [M,H]; all contiguous.
+ */
+int dpk_ffn_swiglu(const void* x, const void* Wg, const void* Wu, const void* Wd,
+                   const uint8_t* mask, void* y, int64_t M, int H, int I, int NG, int dtype,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------- routed attention ---- */
+
+/*
+ * Prefill attention over the active query rows of each head group (reference:
+ * Attention_Head_V3_Host::run, DynamicPruningKernels/include/attention_prefill/v3/
+ * sm12x.cuh:25-169; host wrapper python/attention_prefill/jit.py:223-284).
+ *   Q,O [B,Tq,Hq,D], K,V [B,Tk,Hk,D] contiguous; group g = query heads
+ *   [g*Hq/NG, (g+1)*Hq/NG); query head h reads KV head h / (Hq/Hk).
+ *   sorted_indices [B,Tq,NG] int64 (token index within the batch row), counts [B,NG].
+ *   leftpad: optional [B] uint32 (keys k < leftpad[b] excluded) or NULL.
+ *   causal: keys k <= q + causal_shift are visible (0 = top-left alignment).
+ * Rows of inactive (token, group) pairs are not written: pass O zero-filled
+ * (jit.py:250).  Requirements: D in {64,128}, Hq % NG == 0, Hq % Hk == 0.
+ */
+int dpk_attn_prefill(const void* Q, const void* K, const void* V, const int64_t* sorted_indices,
+                     const int32_t* counts, const uint32_t* leftpad, void* O, int B, int Tq,
+                     int Tk, int Hq, int Hk, int D, int NG, float scale, int causal,
+                     int causal_shift, int dtype, void* stream);
+
+/* Bytes of scratch dpk_attn_decode needs. */
+size_t dpk_attn_decode_workspace_bytes(int B, int Tk, int Hq, int Hk, int D, int NG);
+
+/*
+ * Decode attention, one query token per sequence, split over the KV length and
+ * merged by log-sum-exp (reference: Attention_Head_V0_Host::run,
+ * DynamicPruningKernels/include/attention_decode/v0/sm12x.cuh:23-198; host wrapper
+ * python/attention_decode/jit.py:201-261).  KV heads none of whose query-head groups
+ * are active for a sequence are never read.
+ *   Q,O [B,1,Hq,D], K,V [B,Tk,Hk,D], mask [B,NG] bytes, leftpad optional [B] uint32.
+ * O is fully written (zeros for inactive groups).
+ */
+int dpk_attn_decode(const void* Q, const void* K, const void* V, const uint8_t* mask,
+                    const uint32_t* leftpad, void* O, int B, int Tk, int Hq, int Hk, int D, int NG,
+                    float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DPK_B200_H_ */

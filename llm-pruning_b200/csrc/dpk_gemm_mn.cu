@@ -1,0 +1,444 @@
+// Output-width routed projection on tcgen05 tensor cores (sm_100a).
+//
+// Work decomposition.  A tile is (group g, 128 consecutive entries of g's list of
+// active tokens, one chunk of BN output channels of g).  The tile list is derived
+// on the device from counts[] (no host synchronisation): a persistent grid of one
+// CTA per SM walks it in group-major order, so that the CTAs running at the same
+// time share one group's weight slab in L2.  No CTA exists for inactive work.
+//
+// Per tile, D[128 x N] = A_gathered[128 x K] * W_slab[N x K]^T with N = BN, or
+// N = 2*BN when a second weight is given: the gate rows and the up rows of the same
+// channels sit back to back in one shared-memory B tile, one UMMA of N = 2*BN
+// produces both, and the epilogue writes silu(gate)*up.
+//
+// Warp roles (320 threads):
+//   warps 0-3  epilogue: TMEM -> registers -> activation -> row scatter to D
+//   warp  4    TMA producer of the weight tiles (one lane)
+//   warp  5    UMMA issuer (one lane); also owns the TMEM allocation
+//   warps 6-9  A-row gather: 16-byte cp.async of token rows into the 128B-swizzled
+//              K-major layout UMMA reads, followed by a generic->async proxy fence
+// The accumulator is double buffered in TMEM (2 x 256 columns), so the epilogue of
+// tile i overlaps the main loop of tile i+1.
+//
+// Algorithmic work per launch: 2*K*G flops per active (token, group) pair per weight.
+#include "dpk_host.h"
+#include "dpk_sm100.cuh"
+
+namespace dpk {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kStages = 4;
+constexpr int kAStageBytes = kBM * kBK * 2;         // 16 KiB
+constexpr int kBStageBytes = 256 * kBK * 2;         // 32 KiB
+constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+constexpr int kMnThreads = 320;
+constexpr int kMaxGroups = 2048;
+constexpr int kGatherLag = 2;                       // cp.async groups kept in flight
+constexpr int kTmemCols = 512;
+
+struct MnParams {
+    const uint8_t* A;       // [M, lda] half
+    uint8_t* D;             // [M, ldd] half
+    const int64_t* sidx;    // [M, NG]
+    const int32_t* counts;  // [NG]
+    int64_t lda, ldd;       // elements
+    int64_t M;
+    int K, NG, G;
+    int BN;                 // output channels per tile and weight
+    int n_chunks;           // G / BN
+    int fused;              // second weight present: silu(gate)*up
+    int act;
+    int* status;
+};
+
+constexpr size_t kMnSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes +
+                                (2 * kStages + 4) * sizeof(uint64_t) + 16 +
+                                (kMaxGroups + 1) * sizeof(int);
+
+__device__ __forceinline__ float apply_act(float x, int act)
+{
+    if (act == DPK_ACT_RELU) return fmaxf(x, 0.f);
+    if (act == DPK_ACT_SILU) return silu_f(x);
+    return x;
+}
+
+// Finds the group whose tile range contains `tile` (prefix[g] <= tile < prefix[g+1]).
+__device__ __forceinline__ int find_group(const int* prefix, int ng, int tile)
+{
+    int lo = 0, hi = ng;   // invariant: prefix[lo] <= tile < prefix[hi]
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (prefix[mid] <= tile) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kMnThreads, 1)
+gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2,
+               const MnParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + size_t(kStages) * kStageBytes);
+    uint64_t* empty = full + kStages;
+    uint64_t* tfull = empty + kStages;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* prefix = reinterpret_cast<int*>(tmem_slot + 4);   // [NG + 1]
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int KB = (p.K + kBK - 1) / kBK;
+
+    // ---- set-up --------------------------------------------------------------------
+    if (warp == 0) {
+        // tile prefix over groups: tiles(g) = ceil(count_g / 128) * n_chunks
+        int run = 0;
+        for (int base = 0; base < p.NG; base += 32) {
+            int g = base + lane;
+            int v = 0;
+            if (g < p.NG) {
+                int c = p.counts[g];
+                c = c < 0 ? 0 : c;
+                v = ((c + kBM - 1) / kBM) * p.n_chunks;
+            }
+            int incl = v;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                int o = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += o;
+            }
+            if (g < p.NG) prefix[g + 1] = run + incl;
+            run += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) prefix[0] = 0;
+    }
+    if (warp == 4 && lane == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1 + 128);   // TMA arrive.expect_tx + 128 gather threads
+            mbar_init(&empty[s], 1);        // one tcgen05.commit
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tfull[b], 1);        // one tcgen05.commit
+            mbar_init(&tempty[b], 128);     // 128 epilogue threads
+        }
+        *abort_flag = 0;
+        mbar_init_fence();
+        tma_prefetch_desc(&tmW);
+        if (p.fused) tma_prefetch_desc(&tmW2);
+    }
+    if (warp == 5) tmem_alloc(tmem_slot, kTmemCols);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const int total_tiles = prefix[p.NG];
+    const int BN = p.BN;
+    const int umma_n = p.fused ? 2 * BN : BN;
+
+    if (warp < 4) {
+        // ============================ epilogue ======================================
+        int acc_it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++acc_it) {
+            const int g = find_group(prefix, p.NG, tile);
+            const int u = tile - prefix[g];
+            const int mtile = u / p.n_chunks, nchunk = u - mtile * p.n_chunks;
+            const int cnt = p.counts[g];
+            const int slot = mtile * kBM + warp * 32 + lane;
+            bool valid = slot < cnt;
+            int64_t tok = 0;
+            if (valid) {
+                tok = p.sidx[static_cast<int64_t>(slot) * p.NG + g];
+                if (tok < 0 || tok >= p.M) {
+                    atomicCAS(p.status, 0, DPK_DEV_BAD_INDEX);
+                    valid = false;
+                }
+            }
+            const int ab = acc_it & 1;
+            // the TMEM loads below are warp-collective: leave only as a whole warp
+            const bool got = mbar_wait(&tfull[ab], (acc_it >> 1) & 1, abort_flag, p.status,
+                                       DPK_DEV_TIMEOUT_TMEM_FULL);
+            if (!__all_sync(0xffffffffu, got)) break;
+            tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) +
+                                   static_cast<uint32_t>(ab * 256);
+            uint8_t* out = p.D + (tok * p.ldd + static_cast<int64_t>(g) * p.G +
+                                  static_cast<int64_t>(nchunk) * BN) * 2;
+            if (p.fused) {
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t gate[32], up[32];
+                    if (BN - c >= 32) {
+                        tmem_ld_32x32b_x32(taddr + c, gate);
+                        tmem_ld_32x32b_x32(taddr + BN + c, up);
+                    } else {   // BN == 16
+                        uint32_t g16[16], u16[16];
+                        tmem_ld_32x32b_x16(taddr + c, g16);
+                        tmem_ld_32x32b_x16(taddr + BN + c, u16);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) { gate[i] = g16[i]; up[i] = u16[i]; }
+                    }
+                    tmem_ld_wait();
+                    const int n = (BN - c >= 32) ? 32 : 16;
+                    if (valid) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            if (q * 8 < n) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    float g0 = __uint_as_float(gate[q * 8 + 2 * j]);
+                                    float g1 = __uint_as_float(gate[q * 8 + 2 * j + 1]);
+                                    float u0 = __uint_as_float(up[q * 8 + 2 * j]);
+                                    float u1 = __uint_as_float(up[q * 8 + 2 * j + 1]);
+                                    w[j] = pack_half2<kBf16>(silu_f(g0) * u0, silu_f(g1) * u1);
+                                }
+                                *reinterpret_cast<uint4*>(out + (c + q * 8) * 2) =
+                                    make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        }
+                    }
+                }
+            } else {
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t v[32];
+                    if (BN - c >= 32) {
+                        tmem_ld_32x32b_x32(taddr + c, v);
+                    } else {
+                        uint32_t v16[16];
+                        tmem_ld_32x32b_x16(taddr + c, v16);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[i] = v16[i];
+                    }
+                    tmem_ld_wait();
+                    const int n = (BN - c >= 32) ? 32 : 16;
+                    if (valid) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            if (q * 8 < n) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    float a0 = apply_act(__uint_as_float(v[q * 8 + 2 * j]), p.act);
+                                    float a1 = apply_act(__uint_as_float(v[q * 8 + 2 * j + 1]), p.act);
+                                    w[j] = pack_half2<kBf16>(a0, a1);
+                                }
+                                *reinterpret_cast<uint4*>(out + (c + q * 8) * 2) =
+                                    make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tempty[ab]);
+        }
+    } else if (warp == 4) {
+        // ============================ weight TMA producer ===========================
+        if (lane == 0) {
+            const uint32_t tx_bytes = static_cast<uint32_t>(umma_n) * kBK * 2;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const int g = find_group(prefix, p.NG, tile);
+                const int u = tile - prefix[g];
+                const int nchunk = u % p.n_chunks;
+                const int row0 = g * p.G + nchunk * BN;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(&empty[s], ((it / kStages) & 1) ^ 1, abort_flag, p.status,
+                                   DPK_DEV_TIMEOUT_EMPTY)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sb = smem + size_t(s) * kStageBytes + kAStageBytes;
+                    mbar_arrive_expect_tx(&full[s], tx_bytes);
+                    tma_load_2d(sb, &tmW, &full[s], kb * kBK, row0);
+                    if (p.fused) tma_load_2d(sb + BN * kBK * 2, &tmW2, &full[s], kb * kBK, row0);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ============================ UMMA issuer ===================================
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_f16(kBf16 ? 1 : 0, kBM, umma_n);
+            int it = 0, acc_it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++acc_it) {
+                const int ab = acc_it & 1;
+                if (!mbar_wait(&tempty[ab], ((acc_it >> 1) & 1) ^ 1, abort_flag, p.status,
+                               DPK_DEV_TIMEOUT_TMEM_EMPTY))
+                    break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(ab * 256);
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(&full[s], (it / kStages) & 1, abort_flag, p.status,
+                                   DPK_DEV_TIMEOUT_FULL)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(smem + size_t(s) * kStageBytes);
+                    const uint64_t adesc = umma_desc_k_sw128(sa);
+                    const uint64_t bdesc = umma_desc_k_sw128(sa + kAStageBytes);
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k) {
+                        // 16 elements = 32 bytes further along K inside the swizzle atom
+                        umma_f16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc,
+                                    (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty[s]);
+                }
+                if (ok) umma_commit(&tfull[ab]);
+            }
+        }
+    } else {
+        // ============================ A-row gather ==================================
+        const int gt = threadIdx.x - 6 * 32;     // 0..127
+        const int chunk = gt & 7;                // 16-byte chunk of the 128-byte row
+        const int rsub = gt >> 3;                // 0..15
+        const uint32_t dst_off = static_cast<uint32_t>(rsub * 128 + ((chunk ^ (rsub & 7)) << 4));
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            const int g = find_group(prefix, p.NG, tile);
+            const int u = tile - prefix[g];
+            const int mtile = u / p.n_chunks;
+            const int cnt = p.counts[g];
+            const uint8_t* src_row[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int slot = mtile * kBM + i * 16 + rsub;
+                src_row[i] = nullptr;
+                if (slot < cnt) {
+                    int64_t tok = p.sidx[static_cast<int64_t>(slot) * p.NG + g];
+                    if (tok >= 0 && tok < p.M) src_row[i] = p.A + tok * p.lda * 2;
+                }
+            }
+            for (int kb = 0; kb < KB; ++kb, ++it) {
+                const int s = it % kStages;
+                if (!mbar_wait(&empty[s], ((it / kStages) & 1) ^ 1, abort_flag, p.status,
+                               DPK_DEV_TIMEOUT_EMPTY)) {
+                    ok = false;
+                    break;
+                }
+                const int kcol = kb * kBK + chunk * 8;
+                const bool kvalid = kcol < p.K;
+                const uint32_t dst = smem_u32(smem + size_t(s) * kStageBytes) + dst_off;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const bool on = kvalid && src_row[i] != nullptr;
+                    const void* src = on ? static_cast<const void*>(src_row[i] + kcol * 2)
+                                         : static_cast<const void*>(p.A);
+                    cp_async_16(dst + i * 16 * 128, src, on ? 16u : 0u);
+                }
+                cp_async_commit();
+                if (it >= kGatherLag) {
+                    cp_async_wait<kGatherLag>();
+                    fence_proxy_async_smem();
+                    mbar_arrive(&full[(it - kGatherLag) % kStages]);
+                }
+            }
+        }
+        // drain the groups still in flight
+        cp_async_wait<0>();
+        fence_proxy_async_smem();
+        if (ok) {
+            for (int j = (it > kGatherLag ? it - kGatherLag : 0); j < it; ++j)
+                mbar_arrive(&full[j % kStages]);
+        }
+    }
+
+    // ---- tear-down -----------------------------------------------------------------
+    if (*abort_flag) __nanosleep(2000000);   // let copies already in flight land
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) {
+        __syncwarp();   // lanes 1-31 skipped the role loop: reconverge before the aligned op
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+static int pick_bn(int G, int cap)
+{
+    for (int bn = cap; bn >= 16; bn >>= 1)
+        if (G % bn == 0) return bn;
+    return 0;
+}
+
+}  // namespace dpk
+
+using namespace dpk;
+
+extern "C" int dpk_gemm_mn(const void* A, int64_t lda, const void* W, const void* W2, int64_t ldw,
+                           const int64_t* sorted_indices, const int32_t* counts, void* D,
+                           int64_t ldd, int64_t M, int N, int K, int NG, int dtype, int act,
+                           void* stream)
+{
+    DPK_REQUIRE(A && W && D && sorted_indices && counts, "NULL tensor");
+    DPK_REQUIRE(dtype == DPK_F16 || dtype == DPK_BF16, "dtype must be DPK_F16 or DPK_BF16");
+    DPK_REQUIRE(act >= DPK_ACT_IDENTITY && act <= DPK_ACT_SILU, "unknown activation %d", act);
+    DPK_REQUIRE(M >= 0 && M < (1ll << 31) && N > 0 && K > 0 && NG > 0, "bad shape");
+    DPK_REQUIRE(NG <= kMaxGroups, "NG=%d exceeds %d", NG, kMaxGroups);
+    DPK_REQUIRE(N % NG == 0, "N=%d is not divisible by NG=%d", N, NG);
+    const int G = N / NG;
+    DPK_REQUIRE(G % 16 == 0, "group width G=%d must be a multiple of 16", G);
+    DPK_REQUIRE(K % 8 == 0, "K=%d must be a multiple of 8", K);
+    DPK_REQUIRE(lda >= K && ldw >= K && ldd >= N, "row strides shorter than rows");
+    DPK_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && ldd % 8 == 0, "row strides must be multiples of 8");
+    DPK_REQUIRE(aligned16(A) && aligned16(W) && aligned16(D) && (!W2 || aligned16(W2)),
+                "tensors must be 16-byte aligned");
+    if (M == 0) return DPK_OK;
+
+    const int fused = W2 != nullptr;
+    const int BN = pick_bn(G, fused ? 128 : 256);
+    DPK_REQUIRE(BN >= 16, "no tile width divides G=%d", G);
+
+    CUtensorMap tmW, tmW2;
+    int rc = make_tmap_2d_sw128(&tmW, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldw, kBK, BN);
+    if (rc) return rc;
+    rc = make_tmap_2d_sw128(&tmW2, fused ? W2 : W, (uint64_t)K, (uint64_t)N, (uint64_t)ldw, kBK, BN);
+    if (rc) return rc;
+
+    MnParams p;
+    p.A = static_cast<const uint8_t*>(A);
+    p.D = static_cast<uint8_t*>(D);
+    p.sidx = sorted_indices;
+    p.counts = counts;
+    p.lda = lda;
+    p.ldd = ldd;
+    p.M = M;
+    p.K = K;
+    p.NG = NG;
+    p.G = G;
+    p.BN = BN;
+    p.n_chunks = G / BN;
+    p.fused = fused;
+    p.act = act;
+    p.status = device_status_ptr();
+    if (!p.status) return fail(DPK_ERR_CUDA, "no status word on this device");
+
+    // upper bound of the tile count, known without reading counts[] back
+    int64_t bound = ((M + kBM - 1) / kBM + 1) * (int64_t)NG * p.n_chunks;
+    int grid = sm_count();
+    if (bound < grid) grid = (int)bound;
+    if (grid < 1) grid = 1;
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == DPK_BF16) {
+        DPK_CUDA(cudaFuncSetAttribute(gemm_mn_kernel<true>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMnSmemBytes));
+        gemm_mn_kernel<true><<<grid, kMnThreads, kMnSmemBytes, s>>>(tmW, tmW2, p);
+    } else {
+        DPK_CUDA(cudaFuncSetAttribute(gemm_mn_kernel<false>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMnSmemBytes));
+        gemm_mn_kernel<false><<<grid, kMnThreads, kMnSmemBytes, s>>>(tmW, tmW2, p);
+    }
+    DPK_CUDA(cudaGetLastError());
+    return DPK_OK;
+}

@@ -1,0 +1,281 @@
+// Routing kernels: top-k mask, routing layout (stable active-first compaction per
+// group column), per-column counts of a given layout, packed row / window bits.
+//
+// All of this is integer work bounded by HBM traffic: the byte mask is read twice
+// (M*NG bytes each) and sorted_indices + sorted_mask are written once (9*M*NG
+// bytes).  Reads go through a shared-memory tile so that global accesses are
+// row-contiguous; writes of sorted_indices are 8-byte scatters by construction of
+// the [M,NG] layout the operator API returns.
+#include "dpk_host.h"
+#include "dpk_sm100.cuh"
+
+namespace dpk {
+
+constexpr int kRouteRows = 256;   // rows per CTA tile
+constexpr int kRouteCols = 32;    // group columns per CTA tile
+constexpr int kRouteThreads = 256;
+
+// Loads the [256 x 32] byte tile of `mask` at (r0, c0) into shared memory as 0/1.
+__device__ __forceinline__ void route_load_tile(const uint8_t* __restrict__ mask, int64_t M, int NG,
+                                                int64_t r0, int c0,
+                                                uint8_t (*tile)[kRouteCols + 4])
+{
+    for (int i = threadIdx.x; i < kRouteRows * kRouteCols; i += kRouteThreads) {
+        int row = i / kRouteCols, col = i % kRouteCols;
+        int64_t r = r0 + row;
+        int c = c0 + col;
+        uint8_t v = 0;
+        if (r < M && c < NG) v = mask[r * NG + c] != 0;
+        tile[row][col] = v;
+    }
+}
+
+// pass 1: active rows of every (row block, column)
+__global__ void __launch_bounds__(kRouteThreads)
+route_count_kernel(const uint8_t* __restrict__ mask, int64_t M, int NG, int nrb,
+                   int32_t* __restrict__ block_cnt)
+{
+    __shared__ uint8_t tile[kRouteRows][kRouteCols + 4];
+    const int b = blockIdx.z;
+    const int rb = blockIdx.x;
+    const int c0 = blockIdx.y * kRouteCols;
+    const int64_t r0 = static_cast<int64_t>(rb) * kRouteRows;
+    mask += static_cast<int64_t>(b) * M * NG;
+    route_load_tile(mask, M, NG, r0, c0, tile);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int col = warp; col < kRouteCols; col += kRouteThreads / 32) {
+        int c = c0 + col;
+        if (c >= NG) break;
+        int total = 0;
+        for (int chunk = 0; chunk < kRouteRows / 32; ++chunk) {
+            unsigned bal = __ballot_sync(0xffffffffu, tile[chunk * 32 + lane][col] != 0);
+            total += __popc(bal);
+        }
+        if (lane == 0) block_cnt[(static_cast<int64_t>(b) * nrb + rb) * NG + c] = total;
+    }
+}
+
+// pass 2: exclusive scan over row blocks per column (in place), totals into counts
+__global__ void route_scan_kernel(int32_t* __restrict__ block_cnt, int nrb, int NG, int batches,
+                                  int32_t* __restrict__ counts)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= batches * NG) return;
+    int b = i / NG, c = i % NG;
+    int32_t run = 0;
+    int32_t* p = block_cnt + static_cast<int64_t>(b) * nrb * NG + c;
+    for (int rb = 0; rb < nrb; ++rb) {
+        int32_t v = p[static_cast<int64_t>(rb) * NG];
+        p[static_cast<int64_t>(rb) * NG] = run;
+        run += v;
+    }
+    counts[i] = run;
+}
+
+// pass 3: write the layout
+__global__ void __launch_bounds__(kRouteThreads)
+route_scatter_kernel(const uint8_t* __restrict__ mask, int64_t M, int NG, int nrb,
+                     const int32_t* __restrict__ block_off, const int32_t* __restrict__ counts,
+                     uint8_t* __restrict__ sorted_mask, int64_t* __restrict__ sorted_indices)
+{
+    __shared__ uint8_t tile[kRouteRows][kRouteCols + 4];
+    const int b = blockIdx.z;
+    const int rb = blockIdx.x;
+    const int c0 = blockIdx.y * kRouteCols;
+    const int64_t r0 = static_cast<int64_t>(rb) * kRouteRows;
+    const int64_t boff = static_cast<int64_t>(b) * M * NG;
+    mask += boff;
+    sorted_mask += boff;
+    sorted_indices += boff;
+    counts += static_cast<int64_t>(b) * NG;
+    route_load_tile(mask, M, NG, r0, c0, tile);
+    __syncthreads();
+
+    // sorted_mask: row r of column c is active iff r < counts[c]
+    for (int i = threadIdx.x; i < kRouteRows * kRouteCols; i += kRouteThreads) {
+        int row = i / kRouteCols, col = i % kRouteCols;
+        int64_t r = r0 + row;
+        int c = c0 + col;
+        if (r < M && c < NG) sorted_mask[r * NG + c] = r < counts[c] ? 1 : 0;
+    }
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned lt = (1u << lane) - 1u;
+    for (int col = warp; col < kRouteCols; col += kRouteThreads / 32) {
+        int c = c0 + col;
+        if (c >= NG) break;
+        int64_t act_base = block_off[(static_cast<int64_t>(b) * nrb + rb) * NG + c];
+        int64_t ina_base = static_cast<int64_t>(counts[c]) + (r0 - act_base);
+        for (int chunk = 0; chunk < kRouteRows / 32; ++chunk) {
+            int64_t r = r0 + chunk * 32 + lane;
+            bool valid = r < M;
+            bool on = tile[chunk * 32 + lane][col] != 0;
+            unsigned bal = __ballot_sync(0xffffffffu, on);
+            unsigned val = __ballot_sync(0xffffffffu, valid);
+            unsigned off = val & ~bal;
+            if (valid) {
+                int64_t pos = on ? act_base + __popc(bal & lt) : ina_base + __popc(off & lt);
+                sorted_indices[pos * NG + c] = r;
+            }
+            act_base += __popc(bal);
+            ina_base += __popc(off);
+        }
+    }
+}
+
+// counts of a caller-supplied sorted_mask
+__global__ void __launch_bounds__(256)
+route_counts_kernel(const uint8_t* __restrict__ sorted_mask, int64_t M, int NG,
+                    int32_t* __restrict__ counts)
+{
+    __shared__ int part[8][32];
+    const int b = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * 32 + lane;
+    sorted_mask += static_cast<int64_t>(b) * M * NG;
+    int total = 0;
+    if (c < NG)
+        for (int64_t r = warp; r < M; r += 8) total += sorted_mask[r * NG + c] != 0;
+    part[warp][lane] = total;
+    __syncthreads();
+    if (warp == 0 && c < NG) {
+        int s = 0;
+        for (int w = 0; w < 8; ++w) s += part[w][lane];
+        counts[static_cast<int64_t>(b) * NG + c] = s;
+    }
+}
+
+// packed bits: one CTA per 128-row window
+__global__ void __launch_bounds__(128)
+mask_pack_kernel(const uint8_t* __restrict__ mask, int64_t M, int NG, int words,
+                 uint32_t* __restrict__ row_bits, uint32_t* __restrict__ win_bits)
+{
+    extern __shared__ uint32_t s_or[];   // [4][words]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.x) * 128;
+    for (int w = 0; w < words; ++w) {
+        int g = w * 32 + lane;
+        uint32_t acc = 0;
+        for (int i = warp; i < 128; i += 4) {
+            int64_t r = r0 + i;
+            bool on = (r < M && g < NG) ? (mask[r * NG + g] != 0) : false;
+            uint32_t bits = __ballot_sync(0xffffffffu, on);
+            if (lane == 0 && r < M) row_bits[r * words + w] = bits;
+            acc |= bits;
+        }
+        if (lane == 0) s_or[warp * words + w] = acc;
+    }
+    __syncthreads();
+    for (int w = threadIdx.x; w < words; w += 128)
+        win_bits[static_cast<int64_t>(blockIdx.x) * words + w] =
+            s_or[w] | s_or[words + w] | s_or[2 * words + w] | s_or[3 * words + w];
+}
+
+// top-k mask: one warp per token row; rank by counting, ties to the lower index
+__global__ void __launch_bounds__(128)
+topk_mask_kernel(const float* __restrict__ logits, int64_t M, int NG, int keep,
+                 uint8_t* __restrict__ mask)
+{
+    extern __shared__ float s_l[];   // [4][NG]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * 4 + warp;
+    if (r >= M) return;
+    float* l = s_l + warp * NG;
+    for (int g = lane; g < NG; g += 32) l[g] = logits[r * NG + g];
+    __syncwarp();
+    for (int g = lane; g < NG; g += 32) {
+        float v = l[g];
+        int rank = 0;
+        for (int h = 0; h < NG; ++h) {
+            float u = l[h];
+            rank += (u > v) || (u == v && h < g);
+        }
+        mask[r * NG + g] = rank < keep ? 1 : 0;
+    }
+}
+
+}  // namespace dpk
+
+using namespace dpk;
+
+extern "C" {
+
+int dpk_topk_mask(const float* logits, int64_t M, int NG, int keep, uint8_t* mask, void* stream)
+{
+    DPK_REQUIRE(logits && mask, "logits and mask must not be NULL");
+    DPK_REQUIRE(M >= 0 && NG >= 1 && NG <= 4096, "bad shape M=%lld NG=%d", (long long)M, NG);
+    DPK_REQUIRE(keep >= 0 && keep <= NG, "keep=%d outside [0,%d]", keep, NG);
+    if (M == 0) return DPK_OK;
+    unsigned blocks = static_cast<unsigned>((M + 3) / 4);
+    topk_mask_kernel<<<blocks, 128, 4 * NG * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+        logits, M, NG, keep, mask);
+    DPK_CUDA(cudaGetLastError());
+    return DPK_OK;
+}
+
+size_t dpk_route_workspace_bytes(int batches, int64_t M, int NG)
+{
+    if (batches < 1 || M < 0 || NG < 1) return 0;
+    int64_t nrb = (M + kRouteRows - 1) / kRouteRows;
+    if (nrb < 1) nrb = 1;
+    return static_cast<size_t>(batches) * nrb * NG * sizeof(int32_t);
+}
+
+int dpk_route_compact(const uint8_t* mask, int batches, int64_t M, int NG, uint8_t* sorted_mask,
+                      int64_t* sorted_indices, int32_t* counts, void* workspace,
+                      size_t workspace_bytes, void* stream)
+{
+    DPK_REQUIRE(mask && sorted_mask && sorted_indices && counts, "NULL tensor");
+    DPK_REQUIRE(batches >= 1 && batches <= 65535 && M >= 0 && NG >= 1,
+                "bad shape batches=%d M=%lld NG=%d", batches, (long long)M, NG);
+    DPK_REQUIRE(M < (1ll << 31), "M=%lld too large", (long long)M);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (M == 0) {
+        DPK_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * batches * NG, s));
+        return DPK_OK;
+    }
+    size_t need = dpk_route_workspace_bytes(batches, M, NG);
+    DPK_REQUIRE(workspace && workspace_bytes >= need, "workspace of %zu bytes needed, %zu given",
+                need, workspace_bytes);
+    int nrb = static_cast<int>((M + kRouteRows - 1) / kRouteRows);
+    int ncb = (NG + kRouteCols - 1) / kRouteCols;
+    DPK_REQUIRE(ncb <= 65535, "NG=%d too large", NG);
+    int32_t* block_cnt = static_cast<int32_t*>(workspace);
+    dim3 grid(nrb, ncb, batches);
+    route_count_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt);
+    int total = batches * NG;
+    route_scan_kernel<<<(total + 127) / 128, 128, 0, s>>>(block_cnt, nrb, NG, batches, counts);
+    route_scatter_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt, counts,
+                                                         sorted_mask, sorted_indices);
+    DPK_CUDA(cudaGetLastError());
+    return DPK_OK;
+}
+
+int dpk_route_counts(const uint8_t* sorted_mask, int batches, int64_t M, int NG, int32_t* counts,
+                     void* stream)
+{
+    DPK_REQUIRE(sorted_mask && counts, "NULL tensor");
+    DPK_REQUIRE(batches >= 1 && batches <= 65535 && M >= 0 && NG >= 1, "bad shape");
+    dim3 grid((NG + 31) / 32, batches);
+    route_counts_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(sorted_mask, M, NG,
+                                                                              counts);
+    DPK_CUDA(cudaGetLastError());
+    return DPK_OK;
+}
+
+int dpk_mask_pack(const uint8_t* mask, int64_t M, int NG, uint32_t* row_bits, uint32_t* win_bits,
+                  void* stream)
+{
+    DPK_REQUIRE(mask && row_bits && win_bits, "NULL tensor");
+    DPK_REQUIRE(M >= 0 && NG >= 1 && NG <= 8192, "bad shape M=%lld NG=%d", (long long)M, NG);
+    if (M == 0) return DPK_OK;
+    int words = (NG + 31) / 32;
+    unsigned nwin = static_cast<unsigned>((M + 127) / 128);
+    mask_pack_kernel<<<nwin, 128, 4 * words * sizeof(uint32_t), static_cast<cudaStream_t>(stream)>>>(
+        mask, M, NG, words, row_bits, win_bits);
+    DPK_CUDA(cudaGetLastError());
+    return DPK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,286 @@
+// Device-side building blocks for sm_100a: mbarrier, TMA, tcgen05 (UMMA + TMEM),
+// cp.async, and the shared-memory / instruction descriptors they take.
+//
+// Every wait in this file is bounded.  A wait that runs out records a code in the
+// kernel's status word, raises the CTA-wide abort flag and returns false; callers
+// leave their role loop, meet at the final barrier, release TMEM and return.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dpk {
+
+// ---- status codes written by kernels (0 = fine) ---------------------------------
+enum : int {
+    DPK_DEV_OK = 0,
+    DPK_DEV_TIMEOUT_FULL = 101,     // consumer never saw a filled pipeline stage
+    DPK_DEV_TIMEOUT_EMPTY = 102,    // producer never saw a drained pipeline stage
+    DPK_DEV_TIMEOUT_TMEM_FULL = 103,
+    DPK_DEV_TIMEOUT_TMEM_EMPTY = 104,
+    DPK_DEV_BAD_INDEX = 105,        // a routing index pointed outside the token range
+};
+
+// about one second at 2 GHz
+#ifndef DPK_WAIT_LIMIT_CYCLES
+#define DPK_WAIT_LIMIT_CYCLES (2000000000ll)
+#endif
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31u; }
+
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
+
+// ---- mbarrier ----------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_init_fence()
+{
+    // make the initialised barriers visible to the async proxy (TMA, tcgen05.commit)
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar)
+{
+    asm volatile(
+        "{\n"
+        ".reg .b64 st;\n"
+        "mbarrier.arrive.shared::cta.b64 st, [%0];\n"
+        "}\n" ::"r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+    asm volatile(
+        "{\n"
+        ".reg .b64 st;\n"
+        "mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n"
+        "}\n" ::"r"(smem_u32(bar)),
+        "r"(bytes)
+        : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  `abort_flag` lives in shared memory and is raised by whichever
+// thread of the CTA gives up first, so that the others stop waiting promptly.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > DPK_WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// ---- proxy / tcgen05 fences -------------------------------------------------------
+__device__ __forceinline__ void fence_proxy_async_smem()
+{
+    // generic-proxy writes to shared memory -> visible to the async proxy (UMMA, TMA)
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync()
+{
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after_sync()
+{
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// ---- TMA ---------------------------------------------------------------------------
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+// 2-D tile load global -> shared, completion counted in bytes on `bar`.
+// c0 is the innermost (contiguous) coordinate and must keep c0*elem_size a multiple of 16.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int32_t c0, int32_t c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+// ---- cp.async (16-byte, zero-fill when src_bytes < 16) ----------------------------
+__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gsrc, uint32_t src_bytes)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc),
+                 "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// ---- tensor memory ------------------------------------------------------------------
+// One full warp allocates `ncols` (power of two, 32..512) columns; the base address
+// lands in shared memory at `slot`.
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(slot)),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane
+// (lane-quarter base + i), registers v[0..31] = columns [col, col+32).
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait()
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- UMMA ---------------------------------------------------------------------------
+// Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128
+// bytes (64 half-precision elements) under the 128-byte swizzle: 8-row groups are
+// 1024 bytes apart (stride byte offset), the leading byte offset is unused for
+// swizzled K-major tiles, descriptor version 1 (sm_100), layout type 2 (128B swizzle).
+// The tile base must be 1024-byte aligned.
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);        // start address
+    d |= static_cast<uint64_t>(1) << 16;                            // leading byte offset (unused)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset
+    d |= static_cast<uint64_t>(1) << 46;                            // version
+    d |= static_cast<uint64_t>(2) << 61;                            // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor for kind::f16: fp32 accumulate, A and B both K-major,
+// `half_fmt` 0 = fp16, 1 = bf16, M in {64,128}, N multiple of 16 (M=128) up to 256.
+__host__ __device__ __forceinline__ uint32_t umma_idesc_f16(int half_fmt, int m, int n)
+{
+    uint32_t d = 0;
+    d |= 1u << 4;                                   // D format: f32
+    d |= static_cast<uint32_t>(half_fmt) << 7;      // A format
+    d |= static_cast<uint32_t>(half_fmt) << 10;     // B format
+    d |= static_cast<uint32_t>(n >> 3) << 17;       // N / 8
+    d |= static_cast<uint32_t>(m >> 4) << 24;       // M / 16
+    return d;
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T, issued by one thread.
+__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrive once on `bar` when every UMMA issued so far by this thread has finished
+// (implies tcgen05.fence::before_thread_sync).
+__device__ __forceinline__ void umma_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+
+// ---- small numeric helpers ------------------------------------------------------------
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
+{
+    if constexpr (kBf16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    } else {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+}
+
+}  // namespace dpk

@@ -1,0 +1,95 @@
+"""Dynamic-width SwiGLU FFN with a pre-allocated workspace.
+
+``RoutedFFN`` is the allocation-free form of :func:`dpk_b200.ops.ffn_swiglu`: the
+routing layout, packed routing bits and the intermediate activation live in buffers
+created once, so a forward call only enqueues kernels (route compaction, bit
+packing, fused gate/up projection, down projection) on the current stream.  It is
+what a model wrapper keeps per layer, and what the benchmark times.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from . import _native as N
+from .ops import _dtype_code, _mask_bytes, _need_cuda, _stream
+
+
+class RoutedFFN:
+    """``y = down( mask * silu(gate(x)) * up(x) )`` for ``[M,H]`` tokens.
+
+    Weights: ``gate_weight, up_weight [I,H]``, ``down_weight [H,I]`` (a slice of the
+    full matrices under tensor parallelism), ``num_groups`` routed groups of
+    ``I/num_groups`` channels.  Same mathematics as the reference callers'
+    ``gemm_mn(silu) * gemm_mn -> gemm_k`` (``PruningInferSim/ops/mlp/m_pruning.py:
+    76-105``; ``WIDE/wrapper/attn_group_ffn_block.py:33-38``).
+    """
+
+    def __init__(self, gate_weight: torch.Tensor, up_weight: torch.Tensor,
+                 down_weight: torch.Tensor, num_groups: int, max_tokens: int):
+        dev = _need_cuda(gate_weight, up_weight, down_weight)
+        self.code = _dtype_code(gate_weight)
+        I, H = gate_weight.shape
+        if up_weight.shape != (I, H) or down_weight.shape != (H, I):
+            raise ValueError("weight shapes must be [I,H], [I,H], [H,I]")
+        if I % num_groups:
+            raise ValueError(f"I={I} is not divisible by num_groups={num_groups}")
+        self.H, self.I, self.NG, self.max_tokens = H, I, num_groups, max_tokens
+        self.wg, self.wu, self.wd = (w.contiguous() for w in (gate_weight, up_weight, down_weight))
+        self.device = dev
+        self.lib = N.load()
+        M, NG = max_tokens, num_groups
+        words = (NG + 31) // 32
+        u8, i32, i64 = torch.uint8, torch.int32, torch.int64
+        self.sorted_mask = torch.empty((M, NG), dtype=u8, device=dev)
+        self.sorted_indices = torch.empty((M, NG), dtype=i64, device=dev)
+        self.counts = torch.empty((NG,), dtype=i32, device=dev)
+        self.route_ws_bytes = self.lib.dpk_route_workspace_bytes(1, M, NG)
+        self.route_ws = torch.empty(max(self.route_ws_bytes, 16), dtype=u8, device=dev)
+        self.row_bits = torch.empty((M, words), dtype=i32, device=dev)
+        self.win_bits = torch.empty(((M + 127) // 128, words), dtype=i32, device=dev)
+        self.h = torch.empty((M, I), dtype=gate_weight.dtype, device=dev)
+        self.launches_per_call = 3 + 1 + 1 + 1   # route (3 kernels), bits, gate/up, down
+
+    def __call__(self, x: torch.Tensor, mask: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 events: Optional[Dict[str, List[Tuple[torch.cuda.Event, torch.cuda.Event]]]] = None
+                 ) -> torch.Tensor:
+        """``x``: ``[..., H]``; ``mask``: ``[..., NG]`` (bool / 0-1).  When ``events``
+        is a dict, CUDA event pairs bracketing the two GEMM kernels are appended to
+        ``events["gemm_mn"]`` and ``events["gemm_k"]``."""
+        lead = x.shape[:-1]
+        xf = x.reshape(-1, self.H)
+        if not xf.is_contiguous():
+            xf = xf.contiguous()
+        M = xf.shape[0]
+        if M > self.max_tokens:
+            raise ValueError(f"{M} tokens exceed the planned maximum {self.max_tokens}")
+        m8 = _mask_bytes(mask.reshape(M, self.NG))
+        y = out.view(M, self.H) if out is not None else torch.empty(
+            (M, self.H), dtype=xf.dtype, device=self.device)
+        lib, st, ck = self.lib, _stream(), N.check
+        H, I, NG = self.H, self.I, self.NG
+        ck(lib.dpk_route_compact(m8.data_ptr(), 1, M, NG, self.sorted_mask.data_ptr(),
+                                 self.sorted_indices.data_ptr(), self.counts.data_ptr(),
+                                 self.route_ws.data_ptr(), self.route_ws_bytes, st))
+        ck(lib.dpk_mask_pack(m8.data_ptr(), M, NG, self.row_bits.data_ptr(),
+                             self.win_bits.data_ptr(), st))
+        ev = None
+        if events is not None:
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            ev[0].record()
+        ck(lib.dpk_gemm_mn(xf.data_ptr(), H, self.wg.data_ptr(), self.wu.data_ptr(), H,
+                           self.sorted_indices.data_ptr(), self.counts.data_ptr(), self.h.data_ptr(),
+                           I, M, I, H, NG, self.code, 0, st))
+        if ev is not None:
+            ev[1].record()
+            ev[2].record()
+        ck(lib.dpk_gemm_k(self.h.data_ptr(), I, self.wd.data_ptr(), I, self.row_bits.data_ptr(),
+                          self.win_bits.data_ptr(), y.data_ptr(), H, M, H, I, NG, self.code, st))
+        if ev is not None:
+            ev[3].record()
+            events.setdefault("gemm_mn", []).append((ev[0], ev[1]))
+            events.setdefault("gemm_k", []).append((ev[2], ev[3]))
+        return y.reshape(*lead, self.H)

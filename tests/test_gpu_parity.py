@@ -1,0 +1,443 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle and the golden
+fixtures.  Integer outputs must match bit for bit; floating-point outputs must stay
+within max|err| <= 2e-2 * rms(expected) (bf16 against the fp32 oracle)."""
+
+import numpy as np
+import pytest
+import torch
+
+import golden_io
+from oracle import dpk_oracle as O
+from oracle import route_oracle as RO
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-2   # max-abs error relative to the RMS of the expected output
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from dpk_b200 import build
+    build.build()
+    from dpk_b200 import ops as _ops
+    return _ops
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(ops):
+    yield
+    assert ops.device_status() == 0, "a kernel reported a problem in its status word"
+
+
+def dev(t, dtype=None):
+    t = t.cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def assert_rel(actual, expected, tol=TOL):
+    """Strict form: max|err| <= tol * rms(expected) over the whole output."""
+    err = O.rel_err(actual.float().cpu(), expected)
+    assert err <= tol, f"max-abs error / rms = {err:.4g} > {tol}"
+
+
+def assert_rel_active(actual, expected, tol=TOL):
+    """RMS taken over the entries the routing left non-zero (routed-out blocks are
+    exact zeros on both sides and must stay so)."""
+    a = actual.float().cpu().reshape(expected.shape)
+    err = O.rel_err_active(a, expected)
+    assert err <= tol, f"max-abs error / rms(active) = {err:.4g} > {tol}"
+
+
+def assert_rel_rows(actual, expected, tol=TOL):
+    """Attention: every output row against its own RMS."""
+    err = O.rel_err_rows(actual.float().cpu(), expected)
+    assert err <= tol, f"max over rows of max-abs error / rms(row) = {err:.4g} > {tol}"
+
+
+def assert_ref_tol(actual, expected):
+    """The reference's own kernel-vs-torch tolerance
+    (DynamicPruningKernels/tests/test_gpu_smoke.py:19-20)."""
+    torch.testing.assert_close(actual.float().cpu().reshape(expected.shape), expected,
+                               atol=2e-2, rtol=2e-2)
+
+
+def seeded(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def bf16r(t):
+    return t.to(torch.bfloat16).to(torch.float32)
+
+
+# ------------------------------------------------------------------------ routing
+
+def test_route_compact_golden(ops):
+    z = golden_io.load("routing")
+    smask, sidx, counts = ops.route_compact(dev(z["mask"]))
+    assert torch.equal(smask.cpu(), z["sorted_mask"])
+    assert torch.equal(sidx.cpu(), z["sorted_indices"])
+    assert torch.equal(counts.cpu(), z["counts"])
+
+
+@pytest.mark.parametrize("M,NG,keep", [(8192, 112, 56), (1, 5, 2), (255, 33, 7), (257, 32, 32),
+                                       (1000, 224, 112), (16384, 8, 6), (300, 64, 0)])
+def test_route_compact_random(ops, M, NG, keep):
+    logits = torch.randn(M, NG, generator=seeded(M + NG))
+    mask = O.topk_route_mask(logits, keep)
+    smask, sidx, counts = ops.route_compact(dev(mask))
+    es, ei = torch.sort(mask, dim=0, descending=True, stable=True)
+    assert torch.equal(smask.cpu(), es)
+    assert torch.equal(sidx.cpu(), ei)
+    assert torch.equal(counts.cpu(), mask.sum(0).to(torch.int32))
+    # the same through the C oracle, and counts recovered from a given layout
+    cs, ci, cc = RO.route_compact(mask.numpy())
+    assert np.array_equal(sidx.cpu().numpy(), ci) and np.array_equal(counts.cpu().numpy(), cc)
+    assert torch.equal(ops._counts_of(smask).cpu(), counts.cpu())
+
+
+def test_route_compact_batched(ops):
+    mask = torch.rand(3, 200, 8, generator=seeded(5)) > 0.5
+    smask, sidx, counts = ops.route_compact(dev(mask))
+    es, ei = torch.sort(mask, dim=1, descending=True, stable=True)
+    assert torch.equal(smask.cpu(), es) and torch.equal(sidx.cpu(), ei)
+    assert torch.equal(counts.cpu(), mask.sum(1).to(torch.int32))
+
+
+def test_topk_mask(ops):
+    z = golden_io.load("routing")
+    got = ops.topk_route_mask(dev(z["logits"]), 5).cpu()
+    want = torch.zeros_like(z["mask"])
+    want.scatter_(-1, z["topk5"], True)
+    assert torch.equal(got, want)
+    logits = torch.randn(4, 300, 112, generator=seeded(3))
+    logits[0, 0, :] = 0.5          # ties: lower index wins
+    got = ops.topk_route_mask(dev(logits), 56).cpu()
+    assert torch.equal(got, O.topk_route_mask(logits, 56))
+    assert got[0, 0, :56].all() and not got[0, 0, 56:].any()
+
+
+def test_mask_pack(ops):
+    from dpk_b200 import _native as N
+    mask = torch.rand(1000, 112, generator=seeded(9)) > 0.5
+    mask[128:256] = False
+    m8 = dev(mask).view(torch.uint8)
+    words = 4
+    rb = torch.empty((1000, words), dtype=torch.int32, device="cuda")
+    wb = torch.empty((8, words), dtype=torch.int32, device="cuda")
+    N.check(N.load().dpk_mask_pack(m8.data_ptr(), 1000, 112, rb.data_ptr(), wb.data_ptr(),
+                                   torch.cuda.current_stream().cuda_stream))
+    erb, ewb = RO.row_bits(mask.numpy(), 128)
+    assert np.array_equal(rb.cpu().numpy().view(np.uint32), erb)
+    assert np.array_equal(wb.cpu().numpy().view(np.uint32), ewb)
+
+
+# ------------------------------------------------------------------- routed GEMMs
+
+def test_gemm_mn_golden(ops):
+    z = golden_io.load("ffn_small")
+    bf = torch.bfloat16
+    x, wg, wu, m = dev(z["x"], bf), dev(z["wg"], bf), dev(z["wu"], bf), dev(z["mask"])
+    gate, meta = ops.gemm_mn(x, wg, m, activation="silu")
+    assert set(meta) == {"sorted_mask", "sorted_indices"}
+    assert_rel_active(gate, z["gate"])
+    up, _ = ops.gemm_mn(x, wu, m, sorted_mask=meta["sorted_mask"],
+                        sorted_indices=meta["sorted_indices"])
+    assert_rel_active(up, z["up"])
+    relu, _ = ops.gemm_mn(x, wu, m, activation="relu")
+    assert_rel_active(relu, z["relu"])
+    # inactive blocks are exactly zero
+    G = 512 // 4
+    blk = up.float().cpu().reshape(2, 75, 4, G)
+    assert torch.all(blk[~z["mask"]] == 0)
+    # fused SwiGLU in one pass
+    fused, _ = ops.gemm_mn(x, wg, m, up_weight=wu)
+    assert_rel_active(fused, z["gate"] * z["up"])
+
+
+def test_gemm_k_golden(ops):
+    z = golden_io.load("ffn_small")
+    bf = torch.bfloat16
+    wd, m = dev(z["wd"], bf), dev(z["mask"])
+    down, meta = ops.gemm_k(dev(z["hmid"], bf), wd, m)
+    assert set(meta) == {"sorted_mask", "sorted_indices"}
+    assert_rel(down, z["down"])
+    # whatever sits in the inactive column blocks of A must not contribute
+    down2, _ = ops.gemm_k(dev(z["dense_a"], bf), wd, m)
+    assert_rel_active(down2, z["down_dense_a"])
+    # D is overwritten, not accumulated
+    D = torch.full((2, 75, 128), 7.0, dtype=bf, device="cuda")
+    down3, _ = ops.gemm_k(dev(z["hmid"], bf), wd, m, D=D)
+    assert_rel(down3, z["down"])
+
+
+def test_ffn_golden_and_config1(ops):
+    z = golden_io.load("ffn_small")
+    bf = torch.bfloat16
+    y = ops.ffn_swiglu(dev(z["x"], bf), dev(z["wg"], bf), dev(z["wu"], bf), dev(z["wd"], bf),
+                       dev(z["mask"]))
+    assert_rel(y, z["down"])
+
+    # config 1: hidden 1024, intermediate 4096 as 32 groups of 128, 512 tokens, top-16
+    g = seeded(17)
+    x = bf16r(torch.randn(1, 512, 1024, generator=g))
+    wg = bf16r(torch.randn(4096, 1024, generator=g) * 0.02)
+    wu = bf16r(torch.randn(4096, 1024, generator=g) * 0.02)
+    wd = bf16r(torch.randn(1024, 4096, generator=g) * 0.02)
+    logits = torch.randn(1, 512, 32, generator=g)
+    mask = O.topk_route_mask(logits, 16)
+    got_mask = ops.topk_route_mask(dev(logits), 16)
+    assert torch.equal(got_mask.cpu(), mask)                      # routing bit-exact
+    y = ops.ffn_swiglu(dev(x, bf), dev(wg, bf), dev(wu, bf), dev(wd, bf), got_mask)
+    want = O.ffn_swiglu(x, wg, wu, wd, mask)                       # fp32 reference
+    assert_rel(y, want)
+    # the reference's dense-then-mask formulation agrees too
+    assert_rel(y, O.dense_then_mask_ffn(x, wg, wu, wd, mask))
+    # composition through the four-call API gives the same
+    xd, m = dev(x, bf), dev(mask)
+    gate, meta = ops.gemm_mn(xd, dev(wg, bf), m, activation="silu")
+    up, _ = ops.gemm_mn(xd, dev(wu, bf), m, **meta)
+    y2, _ = ops.gemm_k(gate * up, dev(wd, bf), m, **meta)
+    # three bf16 roundings (gate, up, product) precede the down projection here,
+    # exactly as in the reference's unfused composition
+    assert_rel(y2, want, tol=3e-2)
+
+
+@pytest.mark.parametrize("M,K,N,NG,dtype", [
+    (16, 128, 256, 2, torch.float16),       # the reference's GPU smoke shape
+    (130, 96, 64, 4, torch.bfloat16),       # K tail inside a 64-wide block, G = 16
+    (300, 256, 1024, 1, torch.bfloat16),    # whole-token skip, G = 1024 in 4 chunks
+    (129, 64, 96, 2, torch.float16),        # G = 48
+    (5, 128, 512, 4, torch.bfloat16),       # barely above the GEMV threshold
+    (777, 512, 384, 3, torch.bfloat16),
+])
+def test_gemm_mn_shapes(ops, M, K, N, NG, dtype):
+    g = seeded(M * 7 + N)
+    a = torch.randn(1, M, K, generator=g).to(dtype)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(dtype)
+    mask = torch.rand(1, M, NG, generator=g) > 0.5
+    got, meta = ops.gemm_mn(dev(a), dev(w), dev(mask))
+    assert set(meta) == {"sorted_mask", "sorted_indices"}
+    want = O.gemm_mn(a.float(), w.float(), mask)
+    assert_rel_active(got, want)
+    assert_ref_tol(got, want)
+
+
+@pytest.mark.parametrize("M,K,N,NG,dtype", [
+    (16, 256, 128, 2, torch.float16),       # the reference's GPU smoke shape
+    (130, 512, 72, 4, torch.bfloat16),      # N below one tile, not a multiple of 16
+    (300, 256, 640, 1, torch.bfloat16),     # whole-token skip, N spans 3 chunks
+    (1000, 1024, 256, 16, torch.bfloat16),  # G = 64
+    (257, 384, 128, 3, torch.float16),
+])
+def test_gemm_k_shapes(ops, M, K, N, NG, dtype):
+    g = seeded(M * 3 + K)
+    a = torch.randn(1, M, K, generator=g).to(dtype)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(dtype)
+    mask = torch.rand(1, M, NG, generator=g) > 0.5
+    if M >= 256:
+        mask[0, 128:256] = False            # a window without any active group
+    got, meta = ops.gemm_k(dev(a), dev(w), dev(mask))
+    assert set(meta) == {"sorted_mask", "sorted_indices"}
+    want = O.gemm_k(a.float(), w.float(), mask)
+    assert_rel_active(got, want)
+    assert_ref_tol(got, want)
+
+
+def test_gemm_extreme_masks(ops):
+    g = seeded(4)
+    bf = torch.bfloat16
+    a = torch.randn(1, 200, 128, generator=g).to(bf)
+    w = (torch.randn(256, 128, generator=g) * 0.1).to(bf)
+    wk = (torch.randn(64, 128, generator=g) * 0.1).to(bf)
+    for mask in (torch.zeros(1, 200, 2, dtype=torch.bool), torch.ones(1, 200, 2, dtype=torch.bool)):
+        got, _ = ops.gemm_mn(dev(a), dev(w), dev(mask))
+        assert_rel_active(got, O.gemm_mn(a.float(), w.float(), mask))
+        got, _ = ops.gemm_k(dev(a), dev(wk), dev(mask))
+        assert_rel_active(got, O.gemm_k(a.float(), wk.float(), mask))
+    one = torch.zeros(1, 200, 2, dtype=torch.bool)
+    one[0, 137, 1] = True                    # a single active row
+    got, _ = ops.gemm_mn(dev(a), dev(w), dev(one))
+    assert_rel_active(got, O.gemm_mn(a.float(), w.float(), one))
+    got, _ = ops.gemm_k(dev(a), dev(wk), dev(one))
+    assert_rel_active(got, O.gemm_k(a.float(), wk.float(), one))
+
+
+def test_known_answers_of_the_reference(ops):
+    """DynamicPruningKernels/tests/test_references.py cases (tiny, odd widths: these
+    go down the CUDA-core path).  Inputs are rounded to bf16 first."""
+    z = golden_io.load("ref_known_answers")
+    bf = torch.bfloat16
+    x, ow, dw_, inter = (bf16r(z[k]) for k in ("x", "out_w", "down_w", "inter"))
+    # widths of 8 / 12 are padded to a multiple of 8 elements for 16-byte rows
+    got, _ = ops.gemm_mn(dev(x, bf), dev(ow, bf), dev(z["mask"]))
+    assert_rel_active(got, O.gemm_mn(x, ow, z["mask"]))
+    got, _ = ops.gemm_mn(dev(x, bf), dev(ow, bf), dev(z["tok_mask"]))
+    assert_rel_active(got, O.gemm_mn(x, ow, z["tok_mask"]))
+    pad = torch.zeros(2, 3, 16)
+    pad[..., :12] = inter
+    wpad = torch.zeros(5, 16)
+    wpad[:, :12] = dw_
+    mask4 = torch.cat([z["mask"], torch.zeros(2, 3, 1, dtype=torch.bool)], dim=-1)
+    got, _ = ops.gemm_k(dev(pad, bf), dev(wpad, bf), dev(mask4))
+    assert_rel_active(got, O.gemm_k(inter, dw_, z["mask"]))
+
+
+def test_gemv_dispatch_boundaries(ops):
+    """DynamicPruningKernels/tests/test_gpu_smoke.py:76-201: small-M calls return empty
+    metadata exactly where the reference dispatches to its GEMV kernels."""
+    dt = torch.float16
+    g = seeded(0)
+    w = torch.randn(256, 128, generator=g).to(dt)
+    for M, empty in ((1, True), (4, True), (8, False)):
+        a = torch.randn(1, M, 128, generator=g).to(dt)
+        mask = torch.rand(1, M, 2, generator=g) > 0.5
+        got, meta = ops.gemm_mn(dev(a), dev(w), dev(mask))
+        assert (meta == {}) == empty
+        torch.testing.assert_close(got.float().cpu(), O.gemm_mn(a.float(), w.float(), mask),
+                                   atol=2e-2, rtol=2e-2)
+    for M, K, G, empty in ((1, 256, 128, False), (2, 256, 128, True), (2, 256, 64, False),
+                           (4, 256, 64, True), (4, 128, 32, False), (1, 512, 256, True),
+                           (8, 1024, 512, False)):
+        a = torch.randn(1, M, K, generator=g).to(dt)
+        wk = torch.randn(128, K, generator=g).to(dt) / 8
+        mask = torch.rand(1, M, K // G, generator=g) > 0.5
+        got, meta = ops.gemm_k(dev(a), dev(wk), dev(mask))
+        assert (meta == {}) == empty
+        torch.testing.assert_close(got.float().cpu(), O.gemm_k(a.float(), wk.float(), mask),
+                                   atol=3e-2, rtol=3e-2)
+
+
+def test_config2_sampled_rows(ops):
+    """Llama-3-8B-shaped FFN prefill at full size; rows are independent, so 192 sampled
+    tokens are checked against the fp32 oracle evaluated on those rows only."""
+    dv = "cuda"
+    bf = torch.bfloat16
+    gen = torch.Generator(device=dv).manual_seed(17)
+    M, H, I, NG = 8192, 4096, 14336, 112
+    x = torch.randn(1, M, H, generator=gen, device=dv).to(bf)
+    wg = (torch.randn(I, H, generator=gen, device=dv) * 0.02).to(bf)
+    wu = (torch.randn(I, H, generator=gen, device=dv) * 0.02).to(bf)
+    wd = (torch.randn(H, I, generator=gen, device=dv) * 0.02).to(bf)
+    logits = torch.randn(1, M, NG, generator=gen, device=dv)
+    mask = ops.topk_route_mask(logits, 56)
+    assert torch.equal(mask.cpu(), O.topk_route_mask(logits.cpu(), 56))
+    assert int(mask.sum()) == M * 56
+    y = ops.ffn_swiglu(x, wg, wu, wd, mask)
+    rows = torch.randperm(M, generator=seeded(1))[:192]
+    want = O.ffn_swiglu(x[:, rows].float().cpu(), wg.float().cpu(), wu.float().cpu(),
+                        wd.float().cpu(), mask[:, rows].cpu())
+    assert_rel(y[:, rows], want)
+    # size-independent property: rows whose mask is cleared come out exactly zero
+    mask2 = mask.clone()
+    mask2[0, ::2] = False
+    y2 = ops.ffn_swiglu(x, wg, wu, wd, mask2)
+    assert torch.all(y2[0, ::2] == 0)
+    assert torch.equal(y2[0, 1::2], y[0, 1::2])      # deterministic, row independent
+
+
+# --------------------------------------------------------------------- attention
+
+def test_prefill_golden(ops):
+    z = golden_io.load("attn_prefill_small")
+    bf = torch.bfloat16
+    q, k, v = dev(z["q"], bf), dev(z["k"], bf), dev(z["v"], bf)
+    out, meta = ops.attention_prefill(q, k, v, dev(z["mask2"]))
+    assert set(meta) == {"sorted_mask", "sorted_indices"}
+    assert_rel_rows(out, z["causal_ng2"])
+    reused, _ = ops.attention_prefill(q, k, v, dev(z["mask2"]), **meta)
+    assert torch.equal(reused, out)
+    flat, _ = ops.attention_prefill(q, k, v, dev(z["mask2"]),
+                                    sorted_mask=meta["sorted_mask"].flatten(0, 1),
+                                    sorted_indices=meta["sorted_indices"].flatten(0, 1))
+    assert torch.equal(flat, out)
+    out8, _ = ops.attention_prefill(q, k, v, dev(z["mask8"]))
+    assert_rel_rows(out8, z["causal_ng8"])
+    full, _ = ops.attention_prefill(q, k, v, dev(z["mask2"]), is_causal=False)
+    assert_rel_rows(full, z["full_ng2"])
+    lp, _ = ops.attention_prefill(q, k, v, dev(z["mask2"]), Leftpad=dev(z["leftpad"]))
+    assert_rel_rows(lp, z["causal_ng2_leftpad"])
+    # rows of inactive (token, group) pairs are exactly zero
+    o = out.float().cpu().reshape(2, 83, 2, 4, 64)
+    assert torch.all(o[~z["mask2"]] == 0)
+
+    z = golden_io.load("attn_prefill_d128")
+    out, _ = ops.attention_prefill(dev(z["q"], bf), dev(z["k"], bf), dev(z["v"], bf), dev(z["mask2"]))
+    assert_rel_rows(out, z["causal_ng2"])
+
+
+@pytest.mark.parametrize("B,T,Hq,Hk,D,NG,dtype", [
+    (1, 16, 4, 2, 64, 2, torch.float16),          # the reference's GPU smoke shape
+    (2, 333, 8, 2, 128, 2, torch.bfloat16),
+    (1, 1000, 32, 8, 128, 8, torch.bfloat16),     # benchmark head layout
+    (1, 257, 8, 8, 64, 4, torch.bfloat16),        # groups spanning 2 KV heads
+])
+def test_prefill_random(ops, B, T, Hq, Hk, D, NG, dtype):
+    g = seeded(T + Hq)
+    q = torch.randn(B, T, Hq, D, generator=g).to(dtype)
+    k = torch.randn(B, T, Hk, D, generator=g).to(dtype)
+    v = torch.randn(B, T, Hk, D, generator=g).to(dtype)
+    mask = torch.rand(B, T, NG, generator=g) > 0.5
+    out, _ = ops.attention_prefill(dev(q), dev(k), dev(v), dev(mask))
+    want = O.attention_prefill(q.float(), k.float(), v.float(), mask)
+    assert_rel_rows(out, want)
+    assert_ref_tol(out, want)
+
+
+def test_prefill_metadata_shared_with_gemms(ops):
+    """One routing layout drives attention, the following output projection and a
+    gate-style projection (DynamicPruningKernels/tests/test_gpu_smoke.py:203-292)."""
+    dt = torch.float16
+    g = seeded(0)
+    q = torch.randn(1, 16, 4, 64, generator=g).to(dt)
+    k = torch.randn(1, 16, 2, 64, generator=g).to(dt)
+    v = torch.randn(1, 16, 2, 64, generator=g).to(dt)
+    mask = torch.rand(1, 16, 2, generator=g) > 0.5
+    out, meta = ops.attention_prefill(dev(q), dev(k), dev(v), dev(mask))
+    x = torch.randn(1, 16, 128, generator=g).to(dt)
+    w = torch.randn(256, 128, generator=g).to(dt) / 8
+    got, _ = ops.gemm_mn(dev(x), dev(w), dev(mask), **meta)
+    torch.testing.assert_close(got.float().cpu(), O.gemm_mn(x.float(), w.float(), mask),
+                               atol=2e-2, rtol=2e-2)
+    kin = out.flatten(2)
+    wk = torch.randn(128, 256, generator=g).to(dt) / 8
+    got, _ = ops.gemm_k(kin, dev(wk), dev(mask), **meta)
+    torch.testing.assert_close(got.float().cpu(), O.gemm_k(kin.float().cpu(), wk.float(), mask),
+                               atol=2e-2, rtol=2e-2)
+
+
+def test_decode_golden(ops):
+    z = golden_io.load("attn_decode_small")
+    bf = torch.bfloat16
+    q, k, v = dev(z["q"], bf), dev(z["k"], bf), dev(z["v"], bf)
+    out, meta = ops.attention_decode(q, k, v, dev(z["mask8"]), is_causal=False)
+    assert meta == {}
+    assert_rel_rows(out, z["out_ng8"])
+    out, _ = ops.attention_decode(q, k, v, dev(z["mask16"]), Leftpad=dev(z["leftpad"]),
+                                  is_causal=False)
+    assert_rel_rows(out, z["out_ng16_leftpad"])
+    z = golden_io.load("ref_known_answers")     # reference's Leftpad known answer, D = 8: unsupported
+    with pytest.raises(ValueError, match="head_dim"):
+        ops.attention_decode(dev(z["q"], bf), dev(z["k"], bf), dev(z["v"], bf),
+                             torch.ones(1, 1, 2, dtype=torch.bool, device="cuda"))
+
+
+@pytest.mark.parametrize("B,Tk,Hq,Hk,D,NG", [
+    (1, 32, 16, 8, 128, 8),        # the reference's TileLang smoke shape
+    (4, 5000, 32, 8, 128, 8),      # benchmark head layout, several splits
+    (2, 1025, 8, 8, 64, 8),
+    (3, 700, 16, 4, 128, 2),
+])
+def test_decode_random(ops, B, Tk, Hq, Hk, D, NG):
+    g = seeded(Tk + B)
+    bf = torch.bfloat16
+    q = torch.randn(B, 1, Hq, D, generator=g).to(bf)
+    k = torch.randn(B, Tk, Hk, D, generator=g).to(bf)
+    v = torch.randn(B, Tk, Hk, D, generator=g).to(bf)
+    mask = torch.rand(B, 1, NG, generator=g) > 0.5
+    mask[0, 0, 0] = True
+    out, _ = ops.attention_decode(dev(q), dev(k), dev(v), dev(mask))
+    want = O.attention_decode(q.float(), k.float(), v.float(), mask)
+    assert_rel_rows(out, want)
+    assert_ref_tol(out, want)
+    o = out.float().cpu().reshape(B, NG, -1)
+    assert torch.all(o[~mask.reshape(B, NG)] == 0)
