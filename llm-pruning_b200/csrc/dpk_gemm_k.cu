@@ -234,7 +234,15 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         }
     } else {
         // ============================ row fix-up ====================================
-        const int row = threadIdx.x - 6 * 32;    // 0..127
+        // Warp w owns rows [32w, 32w+32) of the tile.  The rows to clear are found with a
+        // ballot and cleared four per store instruction, eight lanes per 128-byte row
+        // (a lane-per-row loop would put all 32 lanes on the same banks and starve the
+        // tensor core's own operand reads).  The work per stage must stay far below the
+        // 512 cycles the UMMAs of a stage take, since these warps handle stages in order.
+        const int wrow0 = (warp - 6) * 32;
+        const int row = wrow0 + lane;            // 0..127
+        const int sub = lane >> 3;               // which of the 4 rows of a store this lane serves
+        const int chunk = lane & 7;              // 16-byte chunk inside the row
         int it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
@@ -252,18 +260,25 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     const int b = __ffs(bits) - 1;
                     bits &= bits - 1;
                     const bool active = (mine >> b) & 1u;
+                    const unsigned clear = __ballot_sync(0xffffffffu, !active);
                     for (int j = 0; j < p.kb_per_group; ++j, ++it) {
                         const int s = it % kStages;
-                        if (!mbar_wait(&tma_full[s], (it / kStages) & 1, abort_flag, p.status,
-                                       DPK_DEV_TIMEOUT_FULL)) {
+                        const bool got = mbar_wait(&tma_full[s], (it / kStages) & 1, abort_flag,
+                                                   p.status, DPK_DEV_TIMEOUT_FULL);
+                        if (!__all_sync(0xffffffffu, got)) {
                             ok = false;
                             break;
                         }
-                        if (!active) {
-                            uint4* dst = reinterpret_cast<uint4*>(smem + size_t(s) * kStageBytes +
-                                                                  row * 128);
+                        if (clear) {
+                            // 8 stores, each covering rows 4i..4i+3 of the warp's 32 (8 lanes
+                            // per 128-byte row), predicated on the row's bit in `clear`
+                            uint8_t* base = smem + size_t(s) * kStageBytes + (wrow0 + sub) * 128 +
+                                            chunk * 16;
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+                            for (int i = 0; i < 8; ++i)
+                                if ((clear >> (i * 4 + sub)) & 1u)
+                                    *reinterpret_cast<uint4*>(base + i * 4 * 128) =
+                                        make_uint4(0, 0, 0, 0);
                             fence_proxy_async_smem();
                         }
                         mbar_arrive(&full[s]);

@@ -151,7 +151,10 @@ def test_gemm_mn_golden(ops):
     assert torch.all(blk[~z["mask"]] == 0)
     # fused SwiGLU in one pass
     fused, _ = ops.gemm_mn(x, wg, m, up_weight=wu)
-    assert_rel_active(fused, z["gate"] * z["up"])
+    # a product of two Gaussians is heavy tailed: its largest entries sit ~10 rms out,
+    # where half a bf16 ulp (2^-8 relative) alone is 4e-2 rms
+    assert_ref_tol(fused, z["gate"] * z["up"])
+    assert_rel_active(fused, z["gate"] * z["up"], tol=4e-2)
 
 
 def test_gemm_k_golden(ops):
