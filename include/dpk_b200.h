@@ -87,6 +87,30 @@ int dpk_route_compact(const uint8_t* mask, int batches, int64_t M, int NG, uint8
                       size_t workspace_bytes, void* stream);
 
 /*
+ * Same result as dpk_route_compact, for callers that have no way to provide scratch
+ * memory: code that runs where device allocation is off limits (inside a serving loop
+ * whose memory pool is fixed up front, a plugin whose host only lends it the input and
+ * output buffers, a latency path that must not touch the allocator).  The counters the
+ * three kernels exchange live in a 256 KiB array built into the library image, which
+ * every GPU that loads the library holds until the process exits.  This entry point has
+ * no counterpart in the reference, whose hosts allocate their temporaries through
+ * PyTorch on every call.
+ *   - Limit: batches * ceil(M/256) * NG <= 65536 counters (256 KiB); larger problems
+ *     are refused with DPK_ERR_INVALID and a message naming the limit.
+ *   - The first call on each device looks up the array's device address (with that
+ *     device current) and remembers it; make that first call outside any stream capture.
+ *   - It calls no allocating routine: no cudaMalloc / cudaFree, nothing from a tensor
+ *     library.
+ *   - All calls on a device share the one array, which keeps whatever the previous call
+ *     left; each call overwrites every counter it later reads, so nothing needs
+ *     clearing.  Two calls whose kernels overlap on the GPU (different streams, or
+ *     different host threads) race on it: serialise them or use dpk_route_compact.
+ */
+int dpk_route_compact_static(const uint8_t* mask, int batches, int64_t M, int NG,
+                             uint8_t* sorted_mask, int64_t* sorted_indices, int32_t* counts,
+                             void* stream);
+
+/*
  * counts[b,g] = number of non-zero entries of column g of sorted_mask [batches,M,NG].  Used
  * when the caller passes `sorted_mask` / `sorted_indices` from an earlier call
  * (metadata reuse, DynamicPruningKernels/tests/test_gpu_smoke.py:203-292).

@@ -195,6 +195,37 @@ topk_mask_kernel(const float* __restrict__ logits, int64_t M, int NG, int keep,
     }
 }
 
+// ---- scratch for dpk_route_compact_static --------------------------------------------
+// Fixed-size per-(row block, group) counters for callers that cannot hand in a workspace.
+// The array is part of the library image: every GPU that loads the library keeps these
+// 256 KiB until the process exits.
+constexpr size_t kStaticRouteInts = 65536;
+static __device__ __align__(256) int32_t g_route_static_scratch[kStaticRouteInts];
+
+// Device address of the array above for the current device.  The array's name is only a
+// host-side handle in host code, so the address is asked from the runtime once per
+// device (with that device current) and remembered.
+static int route_static_scratch_ptr(int32_t** out)
+{
+    constexpr int kMaxDev = 64;
+    static int32_t* cached[kMaxDev] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess)
+        return fail(DPK_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDev) return fail(DPK_ERR_UNSUPPORTED, "device index %d too large", dev);
+    if (!cached[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_route_static_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(DPK_ERR_CUDA, "cudaGetSymbolAddress(route scratch) failed: %s",
+                        cudaGetErrorString(e));
+        cached[dev] = static_cast<int32_t*>(p);
+    }
+    *out = cached[dev];
+    return DPK_OK;
+}
+
 }  // namespace dpk
 
 using namespace dpk;
@@ -274,6 +305,43 @@ int dpk_mask_pack(const uint8_t* mask, int64_t M, int NG, uint32_t* row_bits, ui
     unsigned nwin = static_cast<unsigned>((M + 127) / 128);
     mask_pack_kernel<<<nwin, 128, 4 * words * sizeof(uint32_t), static_cast<cudaStream_t>(stream)>>>(
         mask, M, NG, words, row_bits, win_bits);
+    DPK_CUDA(cudaGetLastError());
+    return DPK_OK;
+}
+
+int dpk_route_compact_static(const uint8_t* mask, int batches, int64_t M, int NG,
+                             uint8_t* sorted_mask, int64_t* sorted_indices, int32_t* counts,
+                             void* stream)
+{
+    DPK_REQUIRE(mask && sorted_mask && sorted_indices && counts, "NULL tensor");
+    DPK_REQUIRE(batches >= 1 && batches <= 65535 && M >= 0 && NG >= 1,
+                "bad shape batches=%d M=%lld NG=%d", batches, (long long)M, NG);
+    DPK_REQUIRE(M < (1ll << 31), "M=%lld too large", (long long)M);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (M == 0) {
+        DPK_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * batches * NG, s));
+        return DPK_OK;
+    }
+    const size_t need = dpk_route_workspace_bytes(batches, M, NG);
+    DPK_REQUIRE(need <= kStaticRouteInts * sizeof(int32_t),
+                "routing problem needs %zu bytes of scratch but the built-in scratch holds %zu "
+                "(batches * ceil(M/256) * NG must not exceed %zu); use dpk_route_compact with a "
+                "caller workspace instead",
+                need, kStaticRouteInts * sizeof(int32_t), kStaticRouteInts);
+    int32_t* block_cnt = nullptr;
+    int rc = route_static_scratch_ptr(&block_cnt);
+    if (rc) return rc;
+    int nrb = static_cast<int>((M + kRouteRows - 1) / kRouteRows);
+    int ncb = (NG + kRouteCols - 1) / kRouteCols;
+    DPK_REQUIRE(ncb <= 65535, "NG=%d too large", NG);
+    dim3 grid(nrb, ncb, batches);
+    // every counter this call reads is written by the first kernel, so nothing left by an
+    // earlier call needs clearing
+    route_count_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt);
+    int total = batches * NG;
+    route_scan_kernel<<<(total + 127) / 128, 128, 0, s>>>(block_cnt, nrb, NG, batches, counts);
+    route_scatter_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt, counts,
+                                                         sorted_mask, sorted_indices);
     DPK_CUDA(cudaGetLastError());
     return DPK_OK;
 }
