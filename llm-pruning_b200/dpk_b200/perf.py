@@ -1,0 +1,211 @@
+"""Throughput runner for the individual operator families.
+
+Counterpart of the reference's ``run.py --run-type run_throughput``
+(``DynamicPruningKernels/run.py:283-311``; metric definitions
+``python/gemm_mn/jit.py:619-652``, ``python/attention_prefill/jit.py:538-541``): times a
+family on seeded synthetic tensors with CUDA events, next to the dense PyTorch
+equivalent (cuBLAS / SDPA), and prints one JSON line per case with the achieved rate
+and its fraction of the measured roofline.
+
+    python -m dpk_b200.perf --kernel attention_prefill      # BASELINE config 3
+    python -m dpk_b200.perf --kernel attention_decode       # BASELINE config 4 (attention)
+    python -m dpk_b200.perf --kernel ffn_decode             # BASELINE config 4 (FFN, 64 tokens)
+    python -m dpk_b200.perf --kernel gemm_mn | gemm_k | ffn # BASELINE config 2 pieces
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+import torch
+
+from . import ops
+from .ffn import RoutedFFN
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+SEED = 17
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d.get("bf16_tflops_sustained", 1425.8), d.get("hbm_gbs", 6449.1), "measured"
+    return 1400.0, 6650.0, "fallback"
+
+
+def time_ms(fn, reps: int, warmup: int = 3):
+    """Median and 20/80 % quantiles of per-call device time (CUDA events)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    samples = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        samples.append(a.elapsed_time(b))
+    samples.sort()
+    q = lambda f: samples[min(len(samples) - 1, int(f * len(samples)))]
+    return statistics.median(samples), q(0.2), q(0.8)
+
+
+def topk_mask(shape, keep, gen):
+    logits = torch.randn(*shape, generator=gen, device="cuda")
+    return ops.topk_route_mask(logits, keep)
+
+
+def run_prefill(args):
+    B, T, Hq, Hk, D, NG, keep = 1, args.tokens or 8192, 32, 8, 128, 8, 4
+    gen = torch.Generator(device="cuda").manual_seed(SEED)
+    bf = torch.bfloat16
+    q = torch.randn(B, T, Hq, D, generator=gen, device="cuda").to(bf)
+    k = torch.randn(B, T, Hk, D, generator=gen, device="cuda").to(bf)
+    v = torch.randn(B, T, Hk, D, generator=gen, device="cuda").to(bf)
+    mask = topk_mask((B, T, NG), keep, gen)
+    out = torch.zeros_like(q)
+    ms, lo, hi = time_ms(lambda: ops.attention_prefill(q, k, v, mask, O=out), args.reps)
+    # algorithmic flops: 4*D per (active query row, visible key) pair and query head
+    pos = torch.arange(1, T + 1, device="cuda", dtype=torch.float64)
+    pairs = float((mask.to(torch.float64) * pos[None, :, None]).sum()) * (Hq // NG)
+    flops = 4.0 * D * pairs
+    qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    dms, _, _ = time_ms(lambda: torch.nn.functional.scaled_dot_product_attention(
+        qt, kt, vt, is_causal=True, enable_gqa=True), args.reps)
+    peak_tf, _, src = peaks()
+    ach = flops / (ms * 1e-3) / 1e12
+    return {"kernel": "attention_prefill", "workload": f"B={B} T={T} Hq={Hq} Hk={Hk} D={D} causal, "
+            f"top-{keep} of {NG} head groups", "ms": ms, "ms_q20": lo, "ms_q80": hi,
+            "tokens_per_s": B * T / (ms * 1e-3), "algorithmic_tflops": flops / 1e12,
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s",
+                         "frac": ach / peak_tf, "peak_source": src + " sustained bf16"},
+            "dense_sdpa_ms": dms, "speedup_vs_dense": dms / ms}
+
+
+def run_decode(args):
+    B, Tk, Hq, Hk, D, NG, keep = args.batch or 64, args.tokens or 32768, 32, 8, 128, 8, 4
+    gen = torch.Generator(device="cuda").manual_seed(SEED)
+    bf = torch.bfloat16
+    q = torch.randn(B, 1, Hq, D, generator=gen, device="cuda").to(bf)
+    k = torch.randn(B, Tk, Hk, D, generator=gen, device="cuda", dtype=bf)
+    v = torch.randn(B, Tk, Hk, D, generator=gen, device="cuda", dtype=bf)
+    mask = topk_mask((B, 1, NG), keep, gen)
+    out = torch.empty_like(q)
+    ms, lo, hi = time_ms(lambda: ops.attention_decode(q, k, v, mask, O=out), args.reps)
+    active_pairs = int(mask.sum())          # NG == Hk: one group per KV head
+    nbytes = 2.0 * Tk * D * 2 * active_pairs
+    qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    dms, _, _ = time_ms(lambda: torch.nn.functional.scaled_dot_product_attention(
+        qt, kt, vt, is_causal=False, enable_gqa=True), max(3, args.reps // 4))
+    _, peak_gbs, src = peaks()
+    ach = nbytes / (ms * 1e-3) / 1e9
+    return {"kernel": "attention_decode", "workload": f"B={B} Tk={Tk} Hq={Hq} Hk={Hk} D={D}, "
+            f"top-{keep} of {NG} head groups, KV cache {2 * k.numel() * 2 / 2**30:.1f} GiB (> L2)",
+            "tpot_us": ms * 1e3, "ms_q20": lo, "ms_q80": hi, "algorithmic_gbytes": nbytes / 1e9,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak_gbs, "unit": "GB/s",
+                         "frac": ach / peak_gbs, "peak_source": src + " copy bandwidth"},
+            "dense_sdpa_us": dms * 1e3, "speedup_vs_dense": dms / ms}
+
+
+def _ffn_tensors(M, gen, H=4096, I=14336):
+    bf = torch.bfloat16
+    x = torch.randn(1, M, H, generator=gen, device="cuda").to(bf)
+    wg = (torch.randn(I, H, generator=gen, device="cuda") * 0.02).to(bf)
+    wu = (torch.randn(I, H, generator=gen, device="cuda") * 0.02).to(bf)
+    wd = (torch.randn(H, I, generator=gen, device="cuda") * 0.02).to(bf)
+    return x, wg, wu, wd
+
+
+def run_ffn(args, decode=False):
+    M = args.tokens or (64 if decode else 8192)
+    H, I, NG, keep = 4096, 14336, 112, 56
+    gen = torch.Generator(device="cuda").manual_seed(SEED)
+    x, wg, wu, wd = _ffn_tensors(M, gen, H, I)
+    mask = topk_mask((1, M, NG), keep, gen)
+    ffn = RoutedFFN(wg, wu, wd, NG, M)
+    y = torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
+    ms, lo, hi = time_ms(lambda: ffn(x, mask, out=y), args.reps)
+    dms, _, _ = time_ms(lambda: (torch.nn.functional.silu(x @ wg.T) * (x @ wu.T)) @ wd.T, args.reps)
+    peak_tf, peak_gbs, src = peaks()
+    flops = 6.0 * H * 128 * M * keep
+    used = int(mask.any(dim=1).sum())                      # groups some token uses
+    wbytes = 3.0 * H * 128 * 2 * used
+    res = {"kernel": "ffn_decode" if decode else "ffn", "workload": f"M={M} H={H} I={I} "
+           f"NG={NG}x128 top-{keep}", "ms": ms, "ms_q20": lo, "ms_q80": hi,
+           "tokens_per_s": M / (ms * 1e-3), "dense_ms": dms, "speedup_vs_dense": dms / ms}
+    if decode:
+        ach = wbytes / (ms * 1e-3) / 1e9
+        res["roofline"] = {"bound": "hbm", "achieved": ach, "peak": peak_gbs, "unit": "GB/s",
+                           "frac": ach / peak_gbs, "peak_source": src + " copy bandwidth",
+                           "algorithmic_bytes": wbytes}
+    else:
+        ach = flops / (ms * 1e-3) / 1e12
+        res["roofline"] = {"bound": "tensor", "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s",
+                           "frac": ach / peak_tf, "peak_source": src + " sustained bf16"}
+    return res
+
+
+def run_gemm(args, which):
+    M, H, I, NG, keep = args.tokens or 8192, 4096, 14336, 112, 56
+    gen = torch.Generator(device="cuda").manual_seed(SEED)
+    x, wg, wu, wd = _ffn_tensors(M, gen, H, I)
+    mask = topk_mask((1, M, NG), keep, gen)
+    peak_tf, _, src = peaks()
+    if which == "gemm_mn":
+        out = torch.zeros(M, I, dtype=torch.bfloat16, device="cuda")
+        _, meta = ops.gemm_mn(x, wg, mask)
+        ms, lo, hi = time_ms(lambda: ops.gemm_mn(x, wg, mask, D=out, **meta), args.reps)
+        dms, _, _ = time_ms(lambda: x @ wg.T, args.reps)
+        flops = 2.0 * H * 128 * M * keep
+    else:
+        a = torch.randn(1, M, I, generator=gen, device="cuda").to(torch.bfloat16)
+        out = torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
+        _, meta = ops.gemm_k(a, wd, mask)
+        ms, lo, hi = time_ms(lambda: ops.gemm_k(a, wd, mask, D=out, **meta), args.reps)
+        dms, _, _ = time_ms(lambda: a @ wd.T, args.reps)
+        flops = 2.0 * H * 128 * M * keep
+    ach = flops / (ms * 1e-3) / 1e12
+    return {"kernel": which, "workload": f"M={M} H={H} I={I} NG={NG}x128 top-{keep}, through the "
+            "operator API with reused routing metadata", "ms": ms, "ms_q20": lo, "ms_q80": hi,
+            "dense_equiv_tflops": 2.0 * M * H * I / (ms * 1e-3) / 1e12,
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s",
+                         "frac": ach / peak_tf, "peak_source": src + " sustained bf16"},
+            "dense_ms": dms, "speedup_vs_dense": dms / ms}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--kernel", required=True,
+                    choices=["attention_prefill", "attention_decode", "ffn", "ffn_decode",
+                             "gemm_mn", "gemm_k"])
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--tokens", type=int, default=0, help="override the token / KV length")
+    ap.add_argument("--batch", type=int, default=0, help="override the decode batch")
+    args = ap.parse_args(argv)
+    assert torch.cuda.is_available(), "dpk_b200.perf needs a CUDA device"
+    if args.kernel == "attention_prefill":
+        res = run_prefill(args)
+    elif args.kernel == "attention_decode":
+        res = run_decode(args)
+    elif args.kernel == "ffn":
+        res = run_ffn(args)
+    elif args.kernel == "ffn_decode":
+        res = run_ffn(args, decode=True)
+    else:
+        res = run_gemm(args, args.kernel)
+    status = ops.device_status()
+    if status:
+        raise SystemExit(f"a kernel reported status {status}")
+    res["data"] = "synthetic, seed %d" % SEED
+    print(json.dumps(res))
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -444,3 +444,56 @@ def test_decode_random(ops, B, Tk, Hq, Hk, D, NG):
     assert_ref_tol(out, want)
     o = out.float().cpu().reshape(B, NG, -1)
     assert torch.all(o[~mask.reshape(B, NG)] == 0)
+
+
+# --------------------------------------------------------------- wrapper call sites
+
+def test_wide_and_lff_call_sites(ops):
+    """The bodies that replace WrapperMLP / WrapperAttention compute what the reference's
+    wrappers compute densely and then mask (WIDE/wrapper/attn_group_ffn_block.py:28-39,
+    73-97; LFF/router_attn_mlp.py:461-476)."""
+    from dpk_b200 import wide
+
+    bf = torch.bfloat16
+    g = seeded(11)
+    B, S, H, I, gs = 2, 150, 256, 1024, 128
+    gate = torch.nn.Linear(H, I, bias=False)
+    up = torch.nn.Linear(H, I, bias=False)
+    down = torch.nn.Linear(I, H, bias=False)
+    for lin in (gate, up, down):
+        lin.weight.data = bf16r(torch.randn(lin.weight.shape, generator=g) * 0.05)
+    x = bf16r(torch.randn(B, S, H, generator=g))
+    execute_ffn = (torch.rand(B, S, I // gs, generator=g) > 0.5).to(bf)      # 0/1 in bf16
+    mlp = wide.RoutedMLP(gate.cuda().to(bf), up.cuda().to(bf), down.cuda().to(bf), gs, B * S)
+    y = mlp(dev(x, bf), execute_ffn.cuda())
+    h = torch.nn.functional.silu(x @ gate.weight.float().cpu().T) * (x @ up.weight.float().cpu().T)
+    h = (h.reshape(B, S, I // gs, gs) * execute_ffn.float()[..., None]).reshape(B, S, I)
+    assert_rel(y, h @ down.weight.float().cpu().T)
+    y_all = mlp(dev(x, bf))                                                  # execute_ffn=None
+    hd = torch.nn.functional.silu(x @ gate.weight.float().cpu().T) * (x @ up.weight.float().cpu().T)
+    assert_rel(y_all, hd @ down.weight.float().cpu().T)
+    tok_gate = (torch.rand(B, S, generator=g) > 0.5).to(bf)
+    y_tok = wide.token_gated_mlp(mlp, dev(x, bf), tok_gate.cuda())
+    assert_rel_active(y_tok, (hd @ down.weight.float().cpu().T) * tok_gate.float()[..., None])
+
+    Hq, Hk, D = 8, 2, 64
+    q = bf16r(torch.randn(B, S, Hq, D, generator=g))
+    k = bf16r(torch.randn(B, S, Hk, D, generator=g))
+    v = bf16r(torch.randn(B, S, Hk, D, generator=g))
+    execute_attn = (torch.rand(B, S, 2, generator=g) > 0.5).to(bf)
+    out = wide.routed_attention(dev(q, bf), dev(k, bf), dev(v, bf), execute_attn.cuda(),
+                                scaling=D ** -0.5)
+    want = O.attention_prefill(q, k, v, execute_attn != 0)
+    assert_rel_rows(out, want)
+    wo = bf16r(torch.randn(H, Hq * D, generator=g) * 0.05)
+    proj, _ = wide.routed_o_proj(out, dev(wo, bf), execute_attn.cuda())
+    # rows inherit the per-row scales of the attention output: measure row by row
+    assert_rel_rows(proj, out.float().cpu().flatten(2) @ wo.T)
+    wq = bf16r(torch.randn(Hq * D, H, generator=g) * 0.05)
+    qp, meta = wide.routed_q_proj(dev(x, bf), dev(wq, bf), execute_attn.cuda())
+    assert_rel_active(qp, O.gemm_mn(x, wq, execute_attn != 0))
+    # decode step through the same call site
+    qd = bf16r(torch.randn(B, 1, Hq, D, generator=g))
+    ed = torch.tensor([[[1.0, 0.0]], [[1.0, 1.0]]]).to(bf)
+    od = wide.routed_attention(dev(qd, bf), dev(k, bf), dev(v, bf), ed.cuda())
+    assert_rel_rows(od, O.attention_decode(qd, k, v, ed != 0))
