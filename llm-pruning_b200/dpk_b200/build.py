@@ -31,6 +31,7 @@ SOURCES = [
     "dpk_gemv.cu",
     "dpk_ffn.cu",
     "dpk_attn_prefill.cu",
+    "dpk_attn_prefill_tc.cu",
     "dpk_attn_decode.cu",
 ]
 
