@@ -320,8 +320,11 @@ extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw
 
     int BN = 256;
     if (N < 256) BN = ((N + 15) / 16) * 16;
-    const int n_chunks = (N + BN - 1) / BN;
     const int64_t nwin = (M + kBM - 1) / kBM;
+    // Few token windows (decode): narrower output chunks until there is about one tile per
+    // SM, so that the weight matrix is streamed by many CTAs in parallel.
+    while (BN > 32 && BN % 32 == 0 && nwin * ((N + BN - 1) / BN) < sm_count()) BN /= 2;
+    const int n_chunks = (N + BN - 1) / BN;
     DPK_REQUIRE(nwin * n_chunks < (1ll << 31), "too many tiles");
 
     CUtensorMap tmA, tmW;

@@ -497,3 +497,33 @@ def test_wide_and_lff_call_sites(ops):
     ed = torch.tensor([[[1.0, 0.0]], [[1.0, 1.0]]]).to(bf)
     od = wide.routed_attention(dev(qd, bf), dev(k, bf), dev(v, bf), ed.cuda())
     assert_rel_rows(od, O.attention_decode(qd, k, v, ed != 0))
+
+
+def test_routed_decoder_layer_single_rank(ops):
+    """The assembled layer (Q-proj, K/V, routed attention, O-proj, residual, routed FFN,
+    residual) against the same composition of oracle operators."""
+    from dpk_b200.layer import RoutedDecoderLayer
+
+    bf = torch.bfloat16
+    g = seeded(21)
+    T, H, Hq, Hk, D, I, NGF = 300, 256, 8, 2, 64, 1024, 8
+    ws = {n: bf16r(torch.randn(*shp, generator=g) * 0.05) for n, shp in dict(
+        wq=(Hq * D, H), wk=(Hk * D, H), wv=(Hk * D, H), wo=(H, Hq * D),
+        wg=(I, H), wu=(I, H), wd=(H, I)).items()}
+    x = bf16r(torch.randn(1, T, H, generator=g))
+    am = torch.rand(1, T, Hk, generator=g) > 0.3
+    fm = O.topk_route_mask(torch.randn(1, T, NGF, generator=g), 4)
+    layer = RoutedDecoderLayer(*(dev(ws[n], bf) for n in ("wq", "wk", "wv", "wo", "wg", "wu", "wd")),
+                               num_q_heads=Hq, num_kv_heads=Hk, head_dim=D, attn_groups=Hk,
+                               ffn_groups=NGF, max_tokens=T)
+    out = layer(dev(x, bf), dev(am), dev(fm))
+    # oracle with the same bf16 hand-offs between operators
+    q = bf16r(O.gemm_mn(x, ws["wq"], am)).view(1, T, Hq, D)
+    k = bf16r(x @ ws["wk"].T).view(1, T, Hk, D)
+    v = bf16r(x @ ws["wv"].T).view(1, T, Hk, D)
+    a = bf16r(O.attention_prefill(q, k, v, am)).view(1, T, Hq * D)
+    x1 = bf16r(x + bf16r(O.gemm_k(a, ws["wo"], am)))
+    want = x1 + O.ffn_swiglu(x1, ws["wg"], ws["wu"], ws["wd"], fm, round_intermediate=bf)
+    # seven bf16 hand-offs (q, k, v, attention, o-proj, residual, FFN) sit between input
+    # and output; each operator alone is held to 2e-2 by the tests above
+    assert_rel(out, want, tol=3e-2)
