@@ -172,6 +172,9 @@ def run_reference_arm(args, rank, world):
         return
     from oracle import dpk_oracle as O
 
+    # torchrun pins OMP_NUM_THREADS=1 per rank; this arm runs on rank 0 alone and may use
+    # every host core
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     g = torch.Generator().manual_seed(SEED)
     wg = torch.randn(INTER, HID, generator=g) * 0.02
     wu = torch.randn(INTER, HID, generator=g) * 0.02
@@ -214,6 +217,14 @@ def main():
                          "profiler captures only and are named in config.workload)")
     ap.add_argument("--skip-e2e", action="store_true", help="profiler captures only")
     ap.add_argument("--skip-dense", action="store_true", help="profiler captures only")
+    ap.add_argument("--ar-chunks", type=int, default=0,
+                    help="N > 1: token chunks of the down projection whose all-reduces overlap "
+                         "the next chunk's compute (0 = automatic: 4 chunks on 2 GPUs, where the "
+                         "16 MiB pieces still run at bandwidth; 1 beyond, where an 8-rank "
+                         "all-reduce of a small piece is latency bound and chunking measured slower)")
+    ap.add_argument("--sm-margin", type=int, default=-1,
+                    help="N > 1: SMs the persistent GEMM kernels leave to the collective "
+                         "(-1 = automatic: 8 when chunking, else 0)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.tokens != M_TOK:
@@ -254,15 +265,28 @@ def main():
     logits = logits_host.to(device)
     y = torch.empty(M_TOK, HID, dtype=torch.bfloat16, device=device)
 
+    if args.ar_chunks <= 0:
+        args.ar_chunks = 4 if world == 2 else 1
+    chunks = args.ar_chunks if world > 1 else 1
+    if args.sm_margin < 0:
+        args.sm_margin = 8 if chunks > 1 else 0
+    if world > 1:
+        from dpk_b200 import _native
+        _native.check(_native.load().dpk_set_sm_margin(args.sm_margin))
+
     def step(events=None, x_in=x, logits_in=logits, y_out=y):
         mask = ops.topk_route_mask(logits_in, KEEP)              # [M, NG] bool, replicated
-        local = mask[:, groups[0]:groups[1]] if world > 1 else mask
-        ffn(x_in, local, out=y_out, events=events)
-        if world > 1:
-            dist.all_reduce(y_out)
+        if world == 1:
+            ffn(x_in, mask, out=y_out, events=events)
+            return y_out
+        works = []
+        ffn(x_in, mask[:, groups[0]:groups[1]], out=y_out, events=events, row_chunks=chunks,
+            chunk_done=lambda rows: works.append(dist.all_reduce(rows, async_op=True)))
+        for wk in works:
+            wk.wait()
         return y_out
 
-    launches_per_step = 1 + ffn.launches_per_call
+    launches_per_step = 1 + ffn.launches_per_call + (chunks - 1)
 
     # ---- device-resident timing -----------------------------------------------------
     for _ in range(args.warmup):
@@ -317,24 +341,30 @@ def main():
         ev_out = [None, None]
         for i in range(n):
             b = i & 1
-            with torch.cuda.stream(s_in):
-                if ev_cmp[b] is not None:
-                    s_in.wait_event(ev_cmp[b])           # x/logits buffer b is free again
-                xd[b].copy_(xh[b], non_blocking=True)
-                ld[b].copy_(lh[b], non_blocking=True)
-                ev_in[b] = torch.cuda.Event()
-                ev_in[b].record(s_in)
-            s_cmp.wait_event(ev_in[b])
+            if rank == 0:
+                with torch.cuda.stream(s_in):
+                    if ev_cmp[b] is not None:
+                        s_in.wait_event(ev_cmp[b])           # x/logits buffer b is free again
+                    xd[b].copy_(xh[b], non_blocking=True)
+                    ld[b].copy_(lh[b], non_blocking=True)
+                    ev_in[b] = torch.cuda.Event()
+                    ev_in[b].record(s_in)
+                s_cmp.wait_event(ev_in[b])
+            if world > 1:
+                # the inputs enter the node once, on rank 0, and reach the other ranks over NVLink
+                dist.broadcast(xd[b], src=0)
+                dist.broadcast(ld[b], src=0)
             if ev_out[b] is not None:
                 s_cmp.wait_event(ev_out[b])              # y buffer b has been read back
             step(None, xd[b], ld[b], yd[b])
             ev_cmp[b] = torch.cuda.Event()
             ev_cmp[b].record(s_cmp)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_cmp[b])
-                yh[b].copy_(yd[b], non_blocking=True)
-                ev_out[b] = torch.cuda.Event()
-                ev_out[b].record(s_out)
+            if rank == 0:                                # the reduced result is identical on every rank
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_cmp[b])
+                    yh[b].copy_(yd[b], non_blocking=True)
+                    ev_out[b] = torch.cuda.Event()
+                    ev_out[b].record(s_out)
 
     if not args.skip_e2e:
         e2e_loop(args.warmup)
@@ -396,7 +426,9 @@ def main():
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD,
                    "parallelism": "single GPU" if world == 1 else
-                   f"tp{world} by channel groups ({gpr} groups per rank) + NCCL all-reduce of y",
+                   f"tp{world} by channel groups ({gpr} groups per rank) + NCCL all-reduce of y in "
+                   f"{chunks} token chunks overlapping the down projection, {args.sm_margin} SMs "
+                   "left to the collective",
                    "l2": "inputs larger than L2 (x 64 MiB + weights 336 MiB + h 224 MiB per step)",
                    "seed": SEED},
         "roofline": {"kernel": "gemm_mn_kernel (fused gate/up + SwiGLU)", "bound": "tensor",
@@ -411,8 +443,8 @@ def main():
         "e2e": None if e2e_ms_step is None else {
             "value": M_TOK / (e2e_ms_step * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms_step,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "how": "pinned host x+logits -> device, routed FFN, y -> pinned host; "
-                   "double buffered over 3 streams"},
+            "how": "pinned host x+logits -> device (rank 0, then NVLink broadcast when N > 1), "
+                   "routed FFN, y -> pinned host (rank 0); double buffered over 3 streams"},
         "gpu_launches": launches_per_step * args.steps,
     }
     if dense is not None:

@@ -43,6 +43,14 @@ extern "C" {
 /* Library version (major*100 + minor). */
 int dpk_version(void);
 
+/*
+ * The persistent GEMM kernels launch one CTA per SM.  A caller that runs a collective
+ * (NCCL) concurrently with them can leave `sms` SMs free for it; 0 restores the default.
+ * Process-wide setting, not thread safe against concurrent launches.  No counterpart in
+ * the reference, which has no collective in its kernel library.
+ */
+int dpk_set_sm_margin(int sms);
+
 /* Message of the last failing call made by this thread ("" if none). */
 const char* dpk_last_error(void);
 

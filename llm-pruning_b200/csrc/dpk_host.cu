@@ -77,6 +77,7 @@ int make_tmap_2d_plain(CUtensorMap* map, const void* base, uint64_t cols, uint64
 }
 
 static const int kMaxDev = 64;
+static int g_sm_margin = 0;
 
 int sm_count()
 {
@@ -89,7 +90,8 @@ int sm_count()
             n = 148;
         cached[dev] = n;
     }
-    return cached[dev];
+    const int usable = cached[dev] - g_sm_margin;
+    return usable < 1 ? 1 : usable;
 }
 
 __device__ int g_dpk_status = 0;
@@ -112,6 +114,13 @@ int* device_status_ptr()
 extern "C" {
 
 int dpk_version(void) { return 100; }
+
+int dpk_set_sm_margin(int sms)
+{
+    DPK_REQUIRE(sms >= 0 && sms < 128, "margin %d outside [0,128)", sms);
+    dpk::g_sm_margin = sms;
+    return DPK_OK;
+}
 
 const char* dpk_last_error(void) { return dpk::g_err; }
 

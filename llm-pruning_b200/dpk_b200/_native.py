@@ -22,6 +22,7 @@ _vp, _i64, _i32, _sz, _f32 = C.c_void_p, C.c_int64, C.c_int, C.c_size_t, C.c_flo
 # name -> (restype, argtypes); every symbol include/dpk_b200.h declares
 SIGNATURES = {
     "dpk_version": (_i32, []),
+    "dpk_set_sm_margin": (_i32, [_i32]),
     "dpk_last_error": (C.c_char_p, []),
     "dpk_device_status": (_i32, [C.POINTER(_i32), _vp]),
     "dpk_topk_mask": (_i32, [_vp, _i64, _i32, _i32, _vp, _vp]),

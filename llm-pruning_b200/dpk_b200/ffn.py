@@ -9,7 +9,7 @@ what a model wrapper keeps per layer, and what the benchmark times.
 
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Tuple
+from typing import Callable, Dict, List, Optional, Tuple
 
 import torch
 
@@ -54,11 +54,17 @@ class RoutedFFN:
         self.launches_per_call = 3 + 1 + 1 + 1   # route (3 kernels), bits, gate/up, down
 
     def __call__(self, x: torch.Tensor, mask: torch.Tensor, out: Optional[torch.Tensor] = None,
-                 events: Optional[Dict[str, List[Tuple[torch.cuda.Event, torch.cuda.Event]]]] = None
-                 ) -> torch.Tensor:
+                 events: Optional[Dict[str, List[Tuple[torch.cuda.Event, torch.cuda.Event]]]] = None,
+                 row_chunks: int = 1,
+                 chunk_done: Optional[Callable[[torch.Tensor], None]] = None) -> torch.Tensor:
         """``x``: ``[..., H]``; ``mask``: ``[..., NG]`` (bool / 0-1).  When ``events``
         is a dict, CUDA event pairs bracketing the two GEMM kernels are appended to
-        ``events["gemm_mn"]`` and ``events["gemm_k"]``."""
+        ``events["gemm_mn"]`` and ``events["gemm_k"]``.
+
+        ``row_chunks > 1`` runs the down projection in that many token chunks (multiples
+        of 128 rows) and calls ``chunk_done(y_rows)`` after each launch -- the hook a
+        tensor-parallel caller uses to start the all-reduce of a finished chunk while the
+        next one is being computed."""
         lead = x.shape[:-1]
         xf = x.reshape(-1, self.H)
         if not xf.is_contiguous():
@@ -86,8 +92,17 @@ class RoutedFFN:
         if ev is not None:
             ev[1].record()
             ev[2].record()
-        ck(lib.dpk_gemm_k(self.h.data_ptr(), I, self.wd.data_ptr(), I, self.row_bits.data_ptr(),
-                          self.win_bits.data_ptr(), y.data_ptr(), H, M, H, I, NG, self.code, st))
+        words = self.row_bits.shape[1]
+        step = M if row_chunks <= 1 else max(128, ((M + row_chunks - 1) // row_chunks + 127) // 128 * 128)
+        esz = y.element_size()
+        for r0 in range(0, M, step):
+            rows = min(step, M - r0)
+            ck(lib.dpk_gemm_k(self.h.data_ptr() + r0 * I * esz, I, self.wd.data_ptr(), I,
+                              self.row_bits.data_ptr() + r0 * words * 4,
+                              self.win_bits.data_ptr() + (r0 // 128) * words * 4,
+                              y.data_ptr() + r0 * H * esz, H, rows, H, I, NG, self.code, st))
+            if chunk_done is not None:
+                chunk_done(y[r0:r0 + rows])
         if ev is not None:
             ev[3].record()
             events.setdefault("gemm_mn", []).append((ev[0], ev[1]))
