@@ -433,7 +433,11 @@ def main():
                    "seed": SEED},
         "roofline": {"kernel": "gemm_mn_kernel (fused gate/up + SwiGLU)", "bound": "tensor",
                      "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
-                     "peak_source": f"{peak_src} sustained bf16", "traffic": None,
+                     "peak_source": f"{peak_src} sustained bf16",
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch
+                     # (profiles/gemm_kernels_config2_counters.md); scales with the rank's share
+                     "traffic": (1.188224e9 + 1.156e8) / world if M_TOK == 8192 else None,
+                     "traffic_source": "ncu capture of one launch at this size, see profiles/",
                      "algorithmic_flops_per_launch": flops_mn},
         "kernels": {"gemm_mn_ms": k_mn, "gemm_k_ms": k_k,
                     "gemm_k_algorithmic_tflops": flops_k / (k_k * 1e-3) / 1e12,

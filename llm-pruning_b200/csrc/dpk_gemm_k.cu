@@ -27,10 +27,9 @@ namespace dpk {
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
-constexpr int kStages = 4;
 constexpr int kAStageBytes = kBM * kBK * 2;
-constexpr int kBStageBytes = 256 * kBK * 2;
-constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+constexpr int kRingBytes = 4 * (kAStageBytes + 256 * kBK * 2);   // 192 KiB of operand ring
+constexpr int kMaxStages = 12;
 constexpr int kKThreads = 320;
 constexpr int kTmemCols = 512;
 
@@ -46,11 +45,13 @@ struct KParams {
     int words;               // ceil(NG / 32)
     int kb_per_group;        // G / 64
     int total_tiles;
+    int stages;              // ring depth: kRingBytes / stage_bytes, at most kMaxStages
+    int stage_bytes;         // kAStageBytes + BN * 128
     int* status;
 };
 
-constexpr size_t kKSmemBytes = 1024 + size_t(kStages) * kStageBytes +
-                               (3 * kStages + 4) * sizeof(uint64_t) + 16;
+constexpr size_t kKSmemBytes = 1024 + size_t(kRingBytes) +
+                               (3 * kMaxStages + 4) * sizeof(uint64_t) + 16;
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kKThreads, 1)
@@ -60,19 +61,21 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~uintptr_t(1023));
-    uint64_t* tma_full = reinterpret_cast<uint64_t*>(smem + size_t(kStages) * kStageBytes);
-    uint64_t* full = tma_full + kStages;
-    uint64_t* empty = full + kStages;
-    uint64_t* tfull = empty + kStages;
+    uint64_t* tma_full = reinterpret_cast<uint64_t*>(smem + size_t(kRingBytes));
+    uint64_t* full = tma_full + kMaxStages;
+    uint64_t* empty = full + kMaxStages;
+    uint64_t* tfull = empty + kMaxStages;
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const int nst = p.stages;
+    const int stage_bytes = p.stage_bytes;
 
     if (warp == 4 && lane == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < nst; ++s) {
             mbar_init(&tma_full[s], 1);   // arrive.expect_tx by the producer
             mbar_init(&full[s], 128);     // fix-up threads
             mbar_init(&empty[s], 1);      // tcgen05.commit
@@ -158,7 +161,8 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         // ============================ TMA producer ==================================
         if (lane == 0) {
             const uint32_t tx_bytes = static_cast<uint32_t>(kBM + BN) * kBK * 2;
-            int it = 0;
+            int s = 0;
+            uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
                 const int mwin = tile / p.n_chunks, nchunk = tile - mwin * p.n_chunks;
@@ -168,18 +172,18 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     while (ok && bits) {
                         const int g = w * 32 + __ffs(bits) - 1;
                         bits &= bits - 1;
-                        for (int j = 0; j < p.kb_per_group; ++j, ++it) {
-                            const int s = it % kStages;
-                            if (!mbar_wait(&empty[s], ((it / kStages) & 1) ^ 1, abort_flag, p.status,
+                        for (int j = 0; j < p.kb_per_group; ++j) {
+                            if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status,
                                            DPK_DEV_TIMEOUT_EMPTY)) {
                                 ok = false;
                                 break;
                             }
-                            uint8_t* sa = smem + size_t(s) * kStageBytes;
+                            uint8_t* sa = smem + size_t(s) * stage_bytes;
                             const int kcol = g * p.G + j * kBK;
                             mbar_arrive_expect_tx(&tma_full[s], tx_bytes);
                             tma_load_2d(sa, &tmA, &tma_full[s], kcol, mwin * kBM);
                             tma_load_2d(sa + kAStageBytes, &tmW, &tma_full[s], kcol, nchunk * BN);
+                            if (++s == nst) { s = 0; ph ^= 1; }
                         }
                     }
                 }
@@ -189,7 +193,8 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         // ============================ UMMA issuer ===================================
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_f16(kBf16 ? 1 : 0, kBM, BN);
-            int it = 0, acc_it = 0;
+            int s = 0, acc_it = 0;
+            uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
                 const int mwin = tile / p.n_chunks;
@@ -206,9 +211,7 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     uint32_t bits = wb[w];
                     while (ok && bits) {
                         bits &= bits - 1;
-                        for (int j = 0; j < p.kb_per_group; ++j, ++it) {
-                            const int s = it % kStages;
-                            const uint32_t ph = (it / kStages) & 1;
+                        for (int j = 0; j < p.kb_per_group; ++j) {
                             if (!mbar_wait(&tma_full[s], ph, abort_flag, p.status,
                                            DPK_DEV_TIMEOUT_FULL) ||
                                 !mbar_wait(&full[s], ph, abort_flag, p.status, DPK_DEV_TIMEOUT_FULL)) {
@@ -216,7 +219,7 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                                 break;
                             }
                             tc_fence_after_sync();
-                            const uint32_t sa = smem_u32(smem + size_t(s) * kStageBytes);
+                            const uint32_t sa = smem_u32(smem + size_t(s) * stage_bytes);
                             const uint64_t adesc = umma_desc_k_sw128(sa);
                             const uint64_t bdesc = umma_desc_k_sw128(sa + kAStageBytes);
 #pragma unroll
@@ -225,6 +228,7 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                                 first = 1;
                             }
                             umma_commit(&empty[s]);
+                            if (++s == nst) { s = 0; ph ^= 1; }
                         }
                     }
                 }
@@ -243,7 +247,8 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         const int row = wrow0 + lane;            // 0..127
         const int sub = lane >> 3;               // which of the 4 rows of a store this lane serves
         const int chunk = lane & 7;              // 16-byte chunk inside the row
-        int it = 0;
+        int s = 0;
+        uint32_t ph = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
             const int mwin = tile / p.n_chunks;
@@ -261,9 +266,8 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                     bits &= bits - 1;
                     const bool active = (mine >> b) & 1u;
                     const unsigned clear = __ballot_sync(0xffffffffu, !active);
-                    for (int j = 0; j < p.kb_per_group; ++j, ++it) {
-                        const int s = it % kStages;
-                        const bool got = mbar_wait(&tma_full[s], (it / kStages) & 1, abort_flag,
+                    for (int j = 0; j < p.kb_per_group; ++j) {
+                        const bool got = mbar_wait(&tma_full[s], ph, abort_flag,
                                                    p.status, DPK_DEV_TIMEOUT_FULL);
                         if (!__all_sync(0xffffffffu, got)) {
                             ok = false;
@@ -272,7 +276,7 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                         if (clear) {
                             // 8 stores, each covering rows 4i..4i+3 of the warp's 32 (8 lanes
                             // per 128-byte row), predicated on the row's bit in `clear`
-                            uint8_t* base = smem + size_t(s) * kStageBytes + (wrow0 + sub) * 128 +
+                            uint8_t* base = smem + size_t(s) * stage_bytes + (wrow0 + sub) * 128 +
                                             chunk * 16;
 #pragma unroll
                             for (int i = 0; i < 8; ++i)
@@ -282,6 +286,7 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                             fence_proxy_async_smem();
                         }
                         mbar_arrive(&full[s]);
+                        if (++s == nst) { s = 0; ph ^= 1; }
                     }
                 }
             }
@@ -348,6 +353,10 @@ extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw
     p.words = (NG + 31) / 32;
     p.kb_per_group = G / kBK;
     p.total_tiles = (int)(nwin * n_chunks);
+    p.stage_bytes = kAStageBytes + BN * kBK * 2;
+    p.stage_bytes = (p.stage_bytes + 1023) / 1024 * 1024;     // swizzled tiles need 1024-byte bases
+    p.stages = kRingBytes / p.stage_bytes;
+    if (p.stages > kMaxStages) p.stages = kMaxStages;
     p.status = device_status_ptr();
     if (!p.status) return fail(DPK_ERR_CUDA, "no status word on this device");
 

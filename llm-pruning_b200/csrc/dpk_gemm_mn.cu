@@ -28,10 +28,9 @@ namespace dpk {
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
-constexpr int kStages = 4;
-constexpr int kAStageBytes = kBM * kBK * 2;         // 16 KiB
-constexpr int kBStageBytes = 256 * kBK * 2;         // 32 KiB
-constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+constexpr int kAStageBytes = kBM * kBK * 2;         // 16 KiB of gathered token rows
+constexpr int kRingBytes = 4 * (kAStageBytes + 256 * kBK * 2);   // 192 KiB of operand ring
+constexpr int kMaxStages = 12;
 constexpr int kMnThreads = 320;
 constexpr int kMaxGroups = 2048;
 constexpr int kGatherLag = 2;                       // cp.async groups kept in flight
@@ -49,11 +48,13 @@ struct MnParams {
     int n_chunks;           // G / BN
     int fused;              // second weight present: silu(gate)*up
     int act;
+    int stages;             // ring depth: kRingBytes / stage_bytes, at most kMaxStages
+    int stage_bytes;        // kAStageBytes + (UMMA N) * 128
     int* status;
 };
 
-constexpr size_t kMnSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes +
-                                (2 * kStages + 4) * sizeof(uint64_t) + 16 +
+constexpr size_t kMnSmemBytes = 1024 /*alignment slack*/ + size_t(kRingBytes) +
+                                (2 * kMaxStages + 4) * sizeof(uint64_t) + 16 +
                                 (kMaxGroups + 1) * sizeof(int);
 
 __device__ __forceinline__ float apply_act(float x, int act)
@@ -82,9 +83,9 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~uintptr_t(1023));
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + size_t(kStages) * kStageBytes);
-    uint64_t* empty = full + kStages;
-    uint64_t* tfull = empty + kStages;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + size_t(kRingBytes));
+    uint64_t* empty = full + kMaxStages;
+    uint64_t* tfull = empty + kMaxStages;
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -93,6 +94,8 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int KB = (p.K + kBK - 1) / kBK;
+    const int nst = p.stages;
+    const int stage_bytes = p.stage_bytes;
 
     // ---- set-up --------------------------------------------------------------------
     if (warp == 0) {
@@ -118,7 +121,7 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         if (lane == 0) prefix[0] = 0;
     }
     if (warp == 4 && lane == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < nst; ++s) {
             mbar_init(&full[s], 1 + 128);   // TMA arrive.expect_tx + 128 gather threads
             mbar_init(&empty[s], 1);        // one tcgen05.commit
         }
@@ -240,24 +243,24 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         // ============================ weight TMA producer ===========================
         if (lane == 0) {
             const uint32_t tx_bytes = static_cast<uint32_t>(umma_n) * kBK * 2;
-            int it = 0;
+            int s = 0;
+            uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
                 const int g = find_group(prefix, p.NG, tile);
                 const int u = tile - prefix[g];
                 const int nchunk = u % p.n_chunks;
                 const int row0 = g * p.G + nchunk * BN;
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const int s = it % kStages;
-                    if (!mbar_wait(&empty[s], ((it / kStages) & 1) ^ 1, abort_flag, p.status,
-                                   DPK_DEV_TIMEOUT_EMPTY)) {
+                for (int kb = 0; kb < KB; ++kb) {
+                    if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, DPK_DEV_TIMEOUT_EMPTY)) {
                         ok = false;
                         break;
                     }
-                    uint8_t* sb = smem + size_t(s) * kStageBytes + kAStageBytes;
+                    uint8_t* sb = smem + size_t(s) * stage_bytes + kAStageBytes;
                     mbar_arrive_expect_tx(&full[s], tx_bytes);
                     tma_load_2d(sb, &tmW, &full[s], kb * kBK, row0);
                     if (p.fused) tma_load_2d(sb + BN * kBK * 2, &tmW2, &full[s], kb * kBK, row0);
+                    if (++s == nst) { s = 0; ph ^= 1; }
                 }
             }
         }
@@ -265,7 +268,8 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         // ============================ UMMA issuer ===================================
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_f16(kBf16 ? 1 : 0, kBM, umma_n);
-            int it = 0, acc_it = 0;
+            int s = 0, acc_it = 0;
+            uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++acc_it) {
                 const int ab = acc_it & 1;
@@ -274,15 +278,13 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(ab * 256);
-                for (int kb = 0; kb < KB; ++kb, ++it) {
-                    const int s = it % kStages;
-                    if (!mbar_wait(&full[s], (it / kStages) & 1, abort_flag, p.status,
-                                   DPK_DEV_TIMEOUT_FULL)) {
+                for (int kb = 0; kb < KB; ++kb) {
+                    if (!mbar_wait(&full[s], ph, abort_flag, p.status, DPK_DEV_TIMEOUT_FULL)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t sa = smem_u32(smem + size_t(s) * kStageBytes);
+                    const uint32_t sa = smem_u32(smem + size_t(s) * stage_bytes);
                     const uint64_t adesc = umma_desc_k_sw128(sa);
                     const uint64_t bdesc = umma_desc_k_sw128(sa + kAStageBytes);
 #pragma unroll
@@ -292,6 +294,7 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                                     (kb | k) != 0 ? 1u : 0u);
                     }
                     umma_commit(&empty[s]);
+                    if (++s == nst) { s = 0; ph ^= 1; }
                 }
                 if (ok) umma_commit(&tfull[ab]);
             }
@@ -302,7 +305,10 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const int chunk = gt & 7;                // 16-byte chunk of the 128-byte row
         const int rsub = gt >> 3;                // 0..15
         const uint32_t dst_off = static_cast<uint32_t>(rsub * 128 + ((chunk ^ (rsub & 7)) << 4));
-        int it = 0;
+        int it = 0;              // k-blocks issued so far
+        int s = 0;               // stage being filled
+        int s_lag = 0;           // stage whose copies are signalled next (kGatherLag behind)
+        uint32_t ph = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
             const int g = find_group(prefix, p.NG, tile);
@@ -320,15 +326,13 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 }
             }
             for (int kb = 0; kb < KB; ++kb, ++it) {
-                const int s = it % kStages;
-                if (!mbar_wait(&empty[s], ((it / kStages) & 1) ^ 1, abort_flag, p.status,
-                               DPK_DEV_TIMEOUT_EMPTY)) {
+                if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, DPK_DEV_TIMEOUT_EMPTY)) {
                     ok = false;
                     break;
                 }
                 const int kcol = kb * kBK + chunk * 8;
                 const bool kvalid = kcol < p.K;
-                const uint32_t dst = smem_u32(smem + size_t(s) * kStageBytes) + dst_off;
+                const uint32_t dst = smem_u32(smem + size_t(s) * stage_bytes) + dst_off;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const bool on = kvalid && src_row[i] != nullptr;
@@ -337,10 +341,12 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     cp_async_16(dst + i * 16 * 128, src, on ? 16u : 0u);
                 }
                 cp_async_commit();
+                if (++s == nst) { s = 0; ph ^= 1; }
                 if (it >= kGatherLag) {
                     cp_async_wait<kGatherLag>();
                     fence_proxy_async_smem();
-                    mbar_arrive(&full[(it - kGatherLag) % kStages]);
+                    mbar_arrive(&full[s_lag]);
+                    if (++s_lag == nst) s_lag = 0;
                 }
             }
         }
@@ -348,8 +354,10 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         cp_async_wait<0>();
         fence_proxy_async_smem();
         if (ok) {
-            for (int j = (it > kGatherLag ? it - kGatherLag : 0); j < it; ++j)
-                mbar_arrive(&full[j % kStages]);
+            for (int j = (it > kGatherLag ? it - kGatherLag : 0); j < it; ++j) {
+                mbar_arrive(&full[s_lag]);
+                if (++s_lag == nst) s_lag = 0;
+            }
         }
     }
 
@@ -428,6 +436,9 @@ extern "C" int dpk_gemm_mn(const void* A, int64_t lda, const void* W, const void
     p.n_chunks = G / BN;
     p.fused = fused;
     p.act = act;
+    p.stage_bytes = kAStageBytes + (fused ? 2 * BN : BN) * kBK * 2;
+    p.stages = kRingBytes / p.stage_bytes;
+    if (p.stages > kMaxStages) p.stages = kMaxStages;
     p.status = device_status_ptr();
     if (!p.status) return fail(DPK_ERR_CUDA, "no status word on this device");
 

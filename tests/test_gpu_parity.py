@@ -527,3 +527,22 @@ def test_routed_decoder_layer_single_rank(ops):
     # seven bf16 hand-offs (q, k, v, attention, o-proj, residual, FFN) sit between input
     # and output; each operator alone is held to 2e-2 by the tests above
     assert_rel(out, want, tol=3e-2)
+
+
+def test_prefill_cross_length(ops):
+    """Tq != Tk: top-left causal alignment without Leftpad, bottom-right with it -- the two
+    behaviours of the reference's PyTorch path (references.py:123-139)."""
+    bf = torch.bfloat16
+    g = seeded(31)
+    B, Tq, Tk, Hq, Hk, D = 2, 70, 200, 8, 4, 64
+    q = bf16r(torch.randn(B, Tq, Hq, D, generator=g))
+    k = bf16r(torch.randn(B, Tk, Hk, D, generator=g))
+    v = bf16r(torch.randn(B, Tk, Hk, D, generator=g))
+    mask = torch.rand(B, Tq, 4, generator=g) > 0.4
+    out, _ = ops.attention_prefill(dev(q, bf), dev(k, bf), dev(v, bf), dev(mask))
+    assert_rel_rows(out, O.attention_prefill(q, k, v, mask))
+    lp = torch.tensor([7, 0])
+    out, _ = ops.attention_prefill(dev(q, bf), dev(k, bf), dev(v, bf), dev(mask), Leftpad=dev(lp))
+    assert_rel_rows(out, O.attention_prefill(q, k, v, mask, leftpad=lp))
+    out, _ = ops.attention_prefill(dev(q, bf), dev(k, bf), dev(v, bf), dev(mask), is_causal=False)
+    assert_rel_rows(out, O.attention_prefill(q, k, v, mask, is_causal=False))
