@@ -25,7 +25,7 @@ extern "C" int dpk_attn_prefill(const void* Q, const void* K, const void* V,
     DPK_REQUIRE(D == 64 || D == 128, "head_dim %d not supported (64 or 128)", D);
     DPK_REQUIRE(Hq % Hk == 0, "Hq=%d must be a multiple of Hk=%d", Hq, Hk);
     DPK_REQUIRE(Hq % NG == 0, "Hq=%d must be a multiple of NG=%d", Hq, NG);
-    DPK_REQUIRE(B <= 65535 && Hq <= 65535, "grid too large");
+    DPK_REQUIRE(B <= 65535 && (Tq + 127) / 128 <= 65535, "grid too large");
     DPK_REQUIRE(static_cast<int64_t>(B) * Tk < (1ll << 31), "B*Tk too large for the K/V tensor map");
     DPK_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V) && aligned16(O),
                 "tensors must be 16-byte aligned");

@@ -6,8 +6,8 @@
 //                        accumulator in TMEM (double buffered)
 //     P = softmax part   4 warps, one query row per thread: TMEM -> registers, running
 //                        row maximum / sum in registers (no shuffles: a row lives in one
-//                        thread), exp2, bf16, written to shared memory as the next A tile
-//     O += P V           UMMA 128xDx64, A = P (K-major), B = V in its natural [key][d]
+//                        thread), exp2, bf16, written back to TMEM over the S tile
+//     O += P V           UMMA 128xDx64, A = P read from TMEM, B = V in its natural [key][d]
 //                        layout (MN-major descriptor), accumulator in TMEM
 // O is rescaled lazily: the reference maximum of a row only moves when the true maximum
 // has grown by more than 2^8, so most tiles skip the TMEM read-modify-write.  K and V
@@ -16,7 +16,7 @@
 // applied element-wise only on tiles that cross a boundary.
 //
 // Warp roles (192 threads): warps 0-3 softmax + epilogue, warp 4 TMA producer, warp 5
-// UMMA issuer and TMEM owner.  A CTA needs 112 KiB of shared memory and 256 TMEM columns,
+// UMMA issuer and TMEM owner.  A CTA needs 96 KiB of shared memory and 256 TMEM columns,
 // so two CTAs share an SM: while one waits for a tile or runs its softmax, the other
 // keeps the tensor pipe and the exponential unit busy.  All waits are bounded.
 //
@@ -77,6 +77,21 @@ __device__ __forceinline__ void tmem_st_wait()
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]^T: A is read from tensor memory (lane = row, every 32-bit
+// column holds two consecutive K elements of a 16-bit type).
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 __device__ __forceinline__ float tc_exp2(float x)
 {
     float y;
@@ -89,12 +104,10 @@ struct TcSmem {
     static constexpr int kQBytes = kTcBM * D * 2;
     static constexpr int kKBytes = kTcBN * D * 2;      // one K stage
     static constexpr int kVBytes = kTcBN * D * 2;      // one V stage
-    static constexpr int kPBytes = kTcBM * kTcBN * 2;
     static constexpr int kOffQ = 0;
     static constexpr int kOffK = kOffQ + kQBytes;
     static constexpr int kOffV = kOffK + 2 * kKBytes;
-    static constexpr int kOffP = kOffV + 2 * kVBytes;
-    static constexpr int kOffBar = kOffP + kPBytes;
+    static constexpr int kOffBar = kOffV + 2 * kVBytes;
     static constexpr int kTotal = kOffBar + 16 * 8 + 16;   // base must be 1024-byte aligned
 };
 
@@ -109,7 +122,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     uint8_t* sQ = smem + L::kOffQ;
     uint8_t* sK = smem + L::kOffK;
     uint8_t* sV = smem + L::kOffV;
-    uint8_t* sP = smem + L::kOffP;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
     uint64_t* q_full = bars + 0;
     uint64_t* k_full = bars + 1;      // [2]
@@ -123,8 +135,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int mt = gridDim.x - 1 - blockIdx.x;     // heavy (late) tiles first
-    const int h = blockIdx.y, b = blockIdx.z;
+    // blockIdx.x (fastest to be scheduled) walks the heads, blockIdx.y the row tiles from the
+    // last (longest key range under causal masking) to the first: every head's heavy tiles
+    // start first and the light ones fill the tail of the launch
+    const int h = blockIdx.x, b = blockIdx.z;
+    const int mt = gridDim.y - 1 - blockIdx.y;
     const int hpg = p.Hq / p.NG;
     const int g = h / hpg;
     const int kvh = h / (p.Hq / p.Hk);
@@ -278,32 +293,29 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             const float rs = (r0 + r1) + (r2 + r3);
             l_sum = l_sum * alpha + rs;
 
-            // the previous P V must have finished before P is overwritten or O is rescaled
-            if (j > 0) {
+            // O may only be rescaled once the previous P V has finished (rare: the reference
+            // maximum of some row of this warp moved)
+            if (j > 0 && __any_sync(0xffffffffu, moved)) {
                 const bool ok2 = mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status,
                                            DPK_DEV_TIMEOUT_TMEM_EMPTY);
                 if (!__all_sync(0xffffffffu, ok2)) { alive = false; break; }
                 tc_fence_after_sync();
-                if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll 1
-                    for (int c = 0; c < D; c += 32) {
-                        uint32_t v[32];
-                        tmem_ld_32x32b_x32(tmem_o + lane_base + c, v);
-                        tmem_ld_wait();
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_o + lane_base + c, v);
+                    tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        tmem_st_32x32b_x32(tmem_o + lane_base + c, v);
-                    }
-                    tmem_st_wait();
+                    for (int i = 0; i < 32; ++i)
+                        v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tmem_st_32x32b_x32(tmem_o + lane_base + c, v);
                 }
+                tmem_st_wait();
             }
-            // P row -> shared memory: one K-major 128-byte-swizzled block of 64 keys
-#pragma unroll
-            for (int cc = 0; cc < kTcBN / 8; ++cc)
-                *reinterpret_cast<uint4*>(sP + row * 128 + ((cc ^ (row & 7)) << 4)) =
-                    make_uint4(pk[cc * 4], pk[cc * 4 + 1], pk[cc * 4 + 2], pk[cc * 4 + 3]);
-            fence_proxy_async_smem();
+            // P replaces the first 32 columns of this tile's S buffer in TMEM (two keys per
+            // 32-bit column); the P V UMMA reads its A operand from there
+            tmem_st_32x32b_x32(ts, pk);
+            tmem_st_wait();
             tc_fence_before_sync();
             mbar_arrive(p_full);
         }
@@ -401,14 +413,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                     break;
                 }
                 tc_fence_after_sync();
-                // 64 keys = 4 steps of 16: A advances 32 bytes inside the 64-key block, B
-                // advances 16 key rows = 2048 bytes; the d blocks of V are kTcBN*128 bytes apart
+                // 64 keys = 4 steps of 16: B advances 16 key rows = 2048 bytes; the d blocks of V
+                // are kTcBN*128 bytes apart
 #pragma unroll
                 for (int k = 0; k < kTcBN / 16; ++k) {
-                    const uint64_t adesc = umma_desc_k_sw128(smem_u32(sP)) + 2 * k;
                     const uint64_t bdesc =
                         umma_desc_mn_sw128(smem_u32(sV) + s * L::kVBytes + k * 2048, kTcBN * 128);
-                    umma_f16_ss(tmem_o, adesc, bdesc, idesc_o, (j | k) != 0 ? 1u : 0u);
+                    // 16 keys = 8 packed columns of the tile's S/P buffer
+                    umma_f16_ts(tmem_o, tmem_s0 + s * kTcBN + k * 8, bdesc, idesc_o,
+                                (j | k) != 0 ? 1u : 0u);
                 }
                 umma_commit(pv_done);
                 umma_commit(&v_empty[s]);
@@ -434,7 +447,7 @@ static int launch_prefill_tc(const CUtensorMap& tmK, const CUtensorMap& tmV, con
     constexpr size_t smem = TcSmem<D>::kTotal;
     DPK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<D, kBf16>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid((p.Tq + kTcBM - 1) / kTcBM, p.Hq, p.B);
+    dim3 grid(p.Hq, (p.Tq + kTcBM - 1) / kTcBM, p.B);
     attn_prefill_tc_kernel<D, kBf16><<<grid, kTcThreads, smem, s>>>(tmK, tmV, p);
     DPK_CUDA(cudaGetLastError());
     return DPK_OK;
