@@ -48,6 +48,7 @@ struct MnParams {
     int n_chunks;           // G / BN
     int fused;              // second weight present: silu(gate)*up
     int act;
+    int rows_per_block;     // row tiles of one group scheduled back to back (L2 blocking of A)
     int stages;             // ring depth: kRingBytes / stage_bytes, at most kMaxStages
     int stage_bytes;        // kAStageBytes + (UMMA N) * 128
     int* status;
@@ -64,16 +65,42 @@ __device__ __forceinline__ float apply_act(float x, int act)
     return x;
 }
 
-// Finds the group whose tile range contains `tile` (prefix[g] <= tile < prefix[g+1]).
-__device__ __forceinline__ int find_group(const int* prefix, int ng, int tile)
-{
-    int lo = 0, hi = ng;   // invariant: prefix[lo] <= tile < prefix[hi]
-    while (hi - lo > 1) {
-        int mid = (lo + hi) >> 1;
-        if (prefix[mid] <= tile) lo = mid; else hi = mid;
+// Tile order.  Row tile i of every group covers roughly the same token range (the routing
+// keeps a similar fraction of every stretch of tokens), so the schedule walks blocks of R row
+// tiles and, inside a block, the groups: the token rows a block gathers stay L2-resident
+// while all groups use them, and one group's weight slab is shared by the R*n_chunks tiles
+// that run back to back.  Row tiles up to the smallest group's count form this regular part
+// (decoded arithmetically); the few tiles beyond it are appended group by group.
+struct TileMap {
+    const int* ragged_prefix;   // [NG + 1] tiles of group g beyond the regular part
+    int ng, n_chunks, rows_per_block, tmin, regular_total, total;
+
+    __device__ __forceinline__ void decode(int tile, int& g, int& mtile, int& nchunk) const
+    {
+        if (tile < regular_total) {
+            const int per_block = rows_per_block * ng * n_chunks;
+            const int mb = tile / per_block;
+            const int off = tile - mb * per_block;
+            const int rows = min(rows_per_block, tmin - mb * rows_per_block);
+            const int per_group = rows * n_chunks;
+            g = off / per_group;
+            const int rem = off - g * per_group;
+            mtile = mb * rows_per_block + rem / n_chunks;
+            nchunk = rem % n_chunks;
+        } else {
+            const int u0 = tile - regular_total;
+            int lo = 0, hi = ng;   // invariant: ragged_prefix[lo] <= u0 < ragged_prefix[hi]
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (ragged_prefix[mid] <= u0) lo = mid; else hi = mid;
+            }
+            g = lo;
+            const int u = u0 - ragged_prefix[g];
+            mtile = tmin + u / n_chunks;
+            nchunk = u % n_chunks;
+        }
     }
-    return lo;
-}
+};
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kMnThreads, 1)
@@ -89,6 +116,7 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     uint64_t* tempty = tfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* s_tmin = reinterpret_cast<int*>(tmem_slot + 2);
     int* prefix = reinterpret_cast<int*>(tmem_slot + 4);   // [NG + 1]
 
     const int warp = threadIdx.x >> 5;
@@ -99,7 +127,16 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
     // ---- set-up --------------------------------------------------------------------
     if (warp == 0) {
-        // tile prefix over groups: tiles(g) = ceil(count_g / 128) * n_chunks
+        // smallest row-tile count over the groups
+        int tmin = 0x7fffffff;
+        for (int g = lane; g < p.NG; g += 32) {
+            int c = p.counts[g];
+            c = c < 0 ? 0 : c;
+            tmin = min(tmin, (c + kBM - 1) / kBM);
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) tmin = min(tmin, __shfl_xor_sync(0xffffffffu, tmin, d));
+        // prefix of the tiles beyond the regular part: (tiles(g) - tmin) * n_chunks
         int run = 0;
         for (int base = 0; base < p.NG; base += 32) {
             int g = base + lane;
@@ -107,7 +144,7 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if (g < p.NG) {
                 int c = p.counts[g];
                 c = c < 0 ? 0 : c;
-                v = ((c + kBM - 1) / kBM) * p.n_chunks;
+                v = ((c + kBM - 1) / kBM - tmin) * p.n_chunks;
             }
             int incl = v;
 #pragma unroll
@@ -118,7 +155,10 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if (g < p.NG) prefix[g + 1] = run + incl;
             run += __shfl_sync(0xffffffffu, incl, 31);
         }
-        if (lane == 0) prefix[0] = 0;
+        if (lane == 0) {
+            prefix[0] = 0;
+            *s_tmin = tmin;
+        }
     }
     if (warp == 4 && lane == 0) {
         for (int s = 0; s < nst; ++s) {
@@ -139,7 +179,15 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const int total_tiles = prefix[p.NG];
+    TileMap tmap;
+    tmap.ragged_prefix = prefix;
+    tmap.ng = p.NG;
+    tmap.n_chunks = p.n_chunks;
+    tmap.rows_per_block = p.rows_per_block;
+    tmap.tmin = *s_tmin;
+    tmap.regular_total = tmap.tmin * p.NG * p.n_chunks;
+    tmap.total = tmap.regular_total + prefix[p.NG];
+    const int total_tiles = tmap.total;
     const int BN = p.BN;
     const int umma_n = p.fused ? 2 * BN : BN;
 
@@ -147,9 +195,8 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         // ============================ epilogue ======================================
         int acc_it = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++acc_it) {
-            const int g = find_group(prefix, p.NG, tile);
-            const int u = tile - prefix[g];
-            const int mtile = u / p.n_chunks, nchunk = u - mtile * p.n_chunks;
+            int g, mtile, nchunk;
+            tmap.decode(tile, g, mtile, nchunk);
             const int cnt = p.counts[g];
             const int slot = mtile * kBM + warp * 32 + lane;
             bool valid = slot < cnt;
@@ -247,9 +294,8 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const int g = find_group(prefix, p.NG, tile);
-                const int u = tile - prefix[g];
-                const int nchunk = u % p.n_chunks;
+                int g, mtile, nchunk;
+                tmap.decode(tile, g, mtile, nchunk);
                 const int row0 = g * p.G + nchunk * BN;
                 for (int kb = 0; kb < KB; ++kb) {
                     if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, DPK_DEV_TIMEOUT_EMPTY)) {
@@ -311,9 +357,8 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         uint32_t ph = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-            const int g = find_group(prefix, p.NG, tile);
-            const int u = tile - prefix[g];
-            const int mtile = u / p.n_chunks;
+            int g, mtile, nchunk;
+            tmap.decode(tile, g, mtile, nchunk);
             const int cnt = p.counts[g];
             const uint8_t* src_row[8];
 #pragma unroll
@@ -436,6 +481,13 @@ extern "C" int dpk_gemm_mn(const void* A, int64_t lda, const void* W, const void
     p.n_chunks = G / BN;
     p.fused = fused;
     p.act = act;
+    {
+        // a block of R row tiles spans about 2*128*R token rows at a 50 % keep ratio; keep the
+        // rows it gathers (K*2 bytes each) within ~48 MiB so that they stay in L2
+        const int64_t span_rows = (48ll << 20) / (static_cast<int64_t>(K) * 2);
+        int r = static_cast<int>(span_rows / (2 * kBM));
+        p.rows_per_block = r < 4 ? 4 : (r > 4096 ? 4096 : r);
+    }
     p.stage_bytes = kAStageBytes + (fused ? 2 * BN : BN) * kBK * 2;
     p.stages = kRingBytes / p.stage_bytes;
     if (p.stages > kMaxStages) p.stages = kMaxStages;
