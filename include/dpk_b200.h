@@ -163,12 +163,21 @@ int dpk_gemm_mn(const void* A, int64_t lda, const void* W, const void* W2, int64
  *   D[t, n] = sum over active g, j of A[t, g*G + j] * W[n, g*G + j]
  * D is overwritten (the behaviour of the reference's PyTorch path,
  * python/references.py:21-26, 83-86), accumulated in fp32 without atomics.
- *   A [M,K] lda, W [N,K] ldw, D [M,N] ldd; row_bits / win_bits from dpk_mask_pack.
+ *   A [M,K] lda, W [N,K] ldw, D [M,N] ldd; row_bits / win_bits from dpk_mask_pack;
+ *   workspace: see dpk_gemm_k_workspace_bytes (may be NULL).
  * Requirements: G = K/NG a multiple of 64, N % 8 == 0, 16-byte aligned rows.
  */
 int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw, const uint32_t* row_bits,
                const uint32_t* win_bits, void* D, int64_t ldd, int64_t M, int N, int K, int NG,
-               int dtype, void* stream);
+               int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Optional scratch of dpk_gemm_k: with very few token windows (decode, M <= 512) the
+ * group range is split over several CTAs which add fp32 partial sums into this buffer
+ * (zero-filled by the call) before a final conversion.  Returns 0 when the shape never
+ * uses it; passing NULL / 0 to dpk_gemm_k is always allowed and only costs decode speed.
+ */
+size_t dpk_gemm_k_workspace_bytes(int64_t M, int N);
 
 /*
  * Small-batch / odd-shape routed projections on CUDA cores, reading the byte mask

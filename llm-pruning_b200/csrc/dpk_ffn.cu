@@ -6,12 +6,12 @@
 namespace {
 
 struct FfnLayout {
-    size_t sorted_mask, sorted_idx, counts, route_ws, row_bits, win_bits, h, total;
+    size_t sorted_mask, sorted_idx, counts, route_ws, row_bits, win_bits, h, acc, total;
 };
 
 size_t up256(size_t v) { return (v + 255) & ~size_t(255); }
 
-FfnLayout ffn_layout(int64_t M, int I, int NG)
+FfnLayout ffn_layout(int64_t M, int H, int I, int NG)
 {
     FfnLayout L;
     const size_t words = (NG + 31) / 32;
@@ -24,6 +24,7 @@ FfnLayout ffn_layout(int64_t M, int I, int NG)
     L.row_bits = off;    off += up256(size_t(M) * words * sizeof(uint32_t));
     L.win_bits = off;    off += up256(nwin * words * sizeof(uint32_t));
     L.h = off;           off += up256(size_t(M) * I * 2);
+    L.acc = off;         off += up256(dpk_gemm_k_workspace_bytes(M, H));
     L.total = off;
     return L;
 }
@@ -34,9 +35,8 @@ extern "C" {
 
 size_t dpk_ffn_workspace_bytes(int64_t M, int H, int I, int NG)
 {
-    (void)H;
     if (M < 0 || I < 1 || NG < 1) return 0;
-    return ffn_layout(M, I, NG).total;
+    return ffn_layout(M, H, I, NG).total;
 }
 
 int dpk_ffn_swiglu(const void* x, const void* Wg, const void* Wu, const void* Wd,
@@ -47,7 +47,7 @@ int dpk_ffn_swiglu(const void* x, const void* Wg, const void* Wu, const void* Wd
     DPK_REQUIRE(M >= 0 && H > 0 && I > 0 && NG > 0, "bad shape");
     DPK_REQUIRE(I % NG == 0, "I=%d is not divisible by NG=%d", I, NG);
     if (M == 0) return DPK_OK;
-    const FfnLayout L = ffn_layout(M, I, NG);
+    const FfnLayout L = ffn_layout(M, H, I, NG);
     DPK_REQUIRE(workspace && workspace_bytes >= L.total, "workspace of %zu bytes needed, %zu given",
                 L.total, workspace_bytes);
     DPK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0,
@@ -70,7 +70,8 @@ int dpk_ffn_swiglu(const void* x, const void* Wg, const void* Wu, const void* Wd
     rc = dpk_gemm_mn(x, H, Wg, Wu, H, sidx, counts, h, I, M, I, H, NG, dtype, DPK_ACT_IDENTITY,
                      stream);
     if (rc) return rc;
-    return dpk_gemm_k(h, I, Wd, I, row_bits, win_bits, y, H, M, H, I, NG, dtype, stream);
+    return dpk_gemm_k(h, I, Wd, I, row_bits, win_bits, y, H, M, H, I, NG, dtype, ws + L.acc,
+                      up256(dpk_gemm_k_workspace_bytes(M, H)), stream);
 }
 
 }  // extern "C"

@@ -45,6 +45,8 @@ struct KParams {
     int words;               // ceil(NG / 32)
     int kb_per_group;        // G / 64
     int total_tiles;
+    int ksplit;              // splits of the group range (1 = none); > 1 needs acc32
+    float* acc32;            // [M, N] fp32, zero-filled: partial sums of the splits land here
     int stages;              // ring depth: kRingBytes / stage_bytes, at most kMaxStages
     int stage_bytes;         // kAStageBytes + BN * 128
     int* status;
@@ -96,25 +98,48 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     const uint32_t tmem_base = *tmem_slot;
     const int BN = p.BN;
 
-    // Does window `mwin` use any group at all?
-    auto window_any = [&](int mwin) -> bool {
+    // Routing bits of window `mwin`, word `w`, restricted to the groups of K-split `split`.
+    auto win_word = [&](int mwin, int w, int split) -> uint32_t {
+        uint32_t bits = p.win_bits[static_cast<int64_t>(mwin) * p.words + w];
+        if (p.ksplit > 1) {
+            const int g0 = static_cast<int>(static_cast<int64_t>(split) * p.NG / p.ksplit);
+            const int g1 = static_cast<int>(static_cast<int64_t>(split + 1) * p.NG / p.ksplit);
+            const int lo = max(g0 - w * 32, 0), hi = min(g1 - w * 32, 32);
+            if (hi <= lo) return 0u;
+            const uint32_t m_hi = hi >= 32 ? 0xffffffffu : ((1u << hi) - 1u);
+            const uint32_t m_lo = (1u << lo) - 1u;
+            bits &= m_hi & ~m_lo;
+        }
+        return bits;
+    };
+    // Does window `mwin` use any group of this split at all?
+    auto window_any = [&](int mwin, int split) -> bool {
         uint32_t any = 0;
-        for (int w = 0; w < p.words; ++w) any |= p.win_bits[static_cast<int64_t>(mwin) * p.words + w];
+        for (int w = 0; w < p.words; ++w) any |= win_word(mwin, w, split);
         return any != 0;
+    };
+    // tile -> (window, output chunk, K-split); the split is the fastest index
+    auto decode = [&](int tile, int& mwin, int& nchunk, int& split) {
+        split = tile % p.ksplit;
+        const int rest = tile / p.ksplit;
+        mwin = rest / p.n_chunks;
+        nchunk = rest - mwin * p.n_chunks;
     };
 
     if (warp < 4) {
         // ============================ epilogue ======================================
         int acc_it = 0;
         for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
-            const int mwin = tile / p.n_chunks, nchunk = tile - mwin * p.n_chunks;
+            int mwin, nchunk, split;
+            decode(tile, mwin, nchunk, split);
             const int64_t r = static_cast<int64_t>(mwin) * kBM + warp * 32 + lane;
             const bool valid = r < p.M;
             const int n0 = nchunk * BN;
             uint8_t* out = p.D + (r * p.ldd + n0) * 2;
-            if (!window_any(mwin)) {
-                // no group is active for any token of the window: the rows are zero
-                if (valid)
+            if (!window_any(mwin, split)) {
+                // no group (of this split) is active for any token of the window: the rows
+                // are zero; with split accumulation there is nothing to add
+                if (valid && p.acc32 == nullptr)
                     for (int c = 0; c < BN && n0 + c < p.N; c += 8)
                         *reinterpret_cast<uint4*>(out + c * 2) = make_uint4(0, 0, 0, 0);
                 continue;
@@ -138,7 +163,12 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 }
                 tmem_ld_wait();
                 const int n = (BN - c >= 32) ? 32 : 16;
-                if (valid) {
+                if (valid && p.acc32 != nullptr) {
+                    float* acc = p.acc32 + r * p.N + n0 + c;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (i < n && n0 + c + i < p.N) atomicAdd(acc + i, __uint_as_float(v[i]));
+                } else if (valid) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         if (q * 8 < n && n0 + c + q * 8 < p.N) {
@@ -165,10 +195,10 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-                const int mwin = tile / p.n_chunks, nchunk = tile - mwin * p.n_chunks;
-                const uint32_t* wb = p.win_bits + static_cast<int64_t>(mwin) * p.words;
+                int mwin, nchunk, split;
+                decode(tile, mwin, nchunk, split);
                 for (int w = 0; ok && w < p.words; ++w) {
-                    uint32_t bits = wb[w];
+                    uint32_t bits = win_word(mwin, w, split);
                     while (ok && bits) {
                         const int g = w * 32 + __ffs(bits) - 1;
                         bits &= bits - 1;
@@ -197,18 +227,18 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-                const int mwin = tile / p.n_chunks;
-                if (!window_any(mwin)) continue;
+                int mwin, nchunk, split;
+                decode(tile, mwin, nchunk, split);
+                if (!window_any(mwin, split)) continue;
                 const int ab = acc_it & 1;
                 if (!mbar_wait(&tempty[ab], ((acc_it >> 1) & 1) ^ 1, abort_flag, p.status,
                                DPK_DEV_TIMEOUT_TMEM_EMPTY))
                     break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(ab * 256);
-                const uint32_t* wb = p.win_bits + static_cast<int64_t>(mwin) * p.words;
                 uint32_t first = 0;
                 for (int w = 0; ok && w < p.words; ++w) {
-                    uint32_t bits = wb[w];
+                    uint32_t bits = win_word(mwin, w, split);
                     while (ok && bits) {
                         bits &= bits - 1;
                         for (int j = 0; j < p.kb_per_group; ++j) {
@@ -251,14 +281,14 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
         uint32_t ph = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-            const int mwin = tile / p.n_chunks;
+            int mwin, nchunk, split;
+            decode(tile, mwin, nchunk, split);
             const int64_t r = static_cast<int64_t>(mwin) * kBM + row;
             const bool in_range = r < p.M;
-            const uint32_t* wb = p.win_bits + static_cast<int64_t>(mwin) * p.words;
             const uint32_t* rb = p.row_bits + (in_range ? r : 0) * p.words;
             uint32_t next_row = in_range ? rb[0] : 0u;
             for (int w = 0; ok && w < p.words; ++w) {
-                uint32_t bits = wb[w];
+                uint32_t bits = win_word(mwin, w, split);
                 const uint32_t mine = next_row;
                 if (w + 1 < p.words) next_row = in_range ? rb[w + 1] : 0u;
                 while (ok && bits) {
@@ -303,13 +333,33 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     }
 }
 
+// fp32 partial sums -> half output (after a split-K launch)
+template <bool kBf16>
+__global__ void gemm_k_convert_kernel(const float* __restrict__ acc, uint8_t* __restrict__ D,
+                                      int64_t ldd, int64_t M, int N)
+{
+    const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 2;
+    if (i >= M * N) return;
+    const int64_t r = i / N;
+    const int n = static_cast<int>(i - r * N);      // N is even: the pair stays in one row
+    *reinterpret_cast<uint32_t*>(D + (r * ldd + n) * 2) = pack_half2<kBf16>(acc[i], acc[i + 1]);
+}
+
 }  // namespace dpk
 
 using namespace dpk;
 
+extern "C" size_t dpk_gemm_k_workspace_bytes(int64_t M, int N)
+{
+    // split accumulation is only used for a handful of token windows (decode)
+    if (M <= 0 || N <= 0 || M > 4 * kBM) return 0;
+    return static_cast<size_t>(M) * N * sizeof(float);
+}
+
 extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw,
                           const uint32_t* row_bits, const uint32_t* win_bits, void* D, int64_t ldd,
-                          int64_t M, int N, int K, int NG, int dtype, void* stream)
+                          int64_t M, int N, int K, int NG, int dtype, void* workspace,
+                          size_t workspace_bytes, void* stream)
 {
     DPK_REQUIRE(A && W && D && row_bits && win_bits, "NULL tensor");
     DPK_REQUIRE(dtype == DPK_F16 || dtype == DPK_BF16, "dtype must be DPK_F16 or DPK_BF16");
@@ -326,12 +376,20 @@ extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw
     int BN = 256;
     if (N < 256) BN = ((N + 15) / 16) * 16;
     const int64_t nwin = (M + kBM - 1) / kBM;
-    // Few token windows (decode): narrower output chunks until there is about one tile per
-    // SM, so that the weight matrix is streamed by many CTAs in parallel.
-    while (BN > 32 && BN % 32 == 0 && nwin * ((N + BN - 1) / BN) < sm_count()) BN /= 2;
     const int n_chunks = (N + BN - 1) / BN;
-    DPK_REQUIRE(nwin * n_chunks < (1ll << 31), "too many tiles");
-
+    DPK_REQUIRE(nwin * n_chunks < (1ll << 27), "too many tiles");
+    // Few token windows (decode): there are not enough [window x 256] tiles to keep the SMs
+    // streaming weights, so the group range is split over several CTAs per tile which add
+    // their fp32 partial sums into the caller's zero-filled workspace.
+    int ksplit = 1;
+    const size_t ws_need = dpk_gemm_k_workspace_bytes(M, N);
+    if (workspace != nullptr && ws_need != 0 && workspace_bytes >= ws_need && N % 2 == 0 &&
+        nwin * n_chunks * 2 <= sm_count()) {
+        ksplit = static_cast<int>(sm_count() / (nwin * n_chunks));
+        if (ksplit > 16) ksplit = 16;
+        if (ksplit > NG) ksplit = NG;
+        if (ksplit < 1) ksplit = 1;
+    }
     CUtensorMap tmA, tmW;
     int rc = make_tmap_2d_sw128(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, kBK, kBM);
     if (rc) return rc;
@@ -352,7 +410,9 @@ extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw
     p.n_chunks = n_chunks;
     p.words = (NG + 31) / 32;
     p.kb_per_group = G / kBK;
-    p.total_tiles = (int)(nwin * n_chunks);
+    p.total_tiles = (int)(nwin * n_chunks) * ksplit;
+    p.ksplit = ksplit;
+    p.acc32 = ksplit > 1 ? static_cast<float*>(workspace) : nullptr;
     p.stage_bytes = kAStageBytes + BN * kBK * 2;
     p.stage_bytes = (p.stage_bytes + 1023) / 1024 * 1024;     // swizzled tiles need 1024-byte bases
     p.stages = kRingBytes / p.stage_bytes;
@@ -364,6 +424,7 @@ extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw
     if (p.total_tiles < grid) grid = p.total_tiles;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (ksplit > 1) DPK_CUDA(cudaMemsetAsync(workspace, 0, ws_need, s));
     if (dtype == DPK_BF16) {
         DPK_CUDA(cudaFuncSetAttribute(gemm_k_kernel<true>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKSmemBytes));
@@ -372,6 +433,15 @@ extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw
         DPK_CUDA(cudaFuncSetAttribute(gemm_k_kernel<false>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKSmemBytes));
         gemm_k_kernel<false><<<grid, kKThreads, kKSmemBytes, s>>>(tmA, tmW, p);
+    }
+    if (ksplit > 1) {
+        const int64_t pairs = (M * N + 1) / 2;
+        const unsigned blocks = static_cast<unsigned>((pairs + 255) / 256);
+        uint8_t* d = static_cast<uint8_t*>(D);
+        if (dtype == DPK_BF16)
+            gemm_k_convert_kernel<true><<<blocks, 256, 0, s>>>(p.acc32, d, ldd, M, N);
+        else
+            gemm_k_convert_kernel<false><<<blocks, 256, 0, s>>>(p.acc32, d, ldd, M, N);
     }
     DPK_CUDA(cudaGetLastError());
     return DPK_OK;

@@ -449,17 +449,8 @@ extern "C" int dpk_gemm_mn(const void* A, int64_t lda, const void* W, const void
     if (M == 0) return DPK_OK;
 
     const int fused = W2 != nullptr;
-    int BN = pick_bn(G, fused ? 128 : 256);
+    const int BN = pick_bn(G, fused ? 128 : 256);
     DPK_REQUIRE(BN >= 16, "no tile width divides G=%d", G);
-    // Few tokens (decode): the launch is bound by streaming the weights once, so use
-    // narrower tiles until there are about two per SM to pull them in parallel.
-    {
-        const int64_t row_tiles = (M + kBM - 1) / kBM;
-        while (BN > 32 && G % (BN / 2) == 0 &&
-               row_tiles * NG * (G / BN) < 2ll * sm_count())
-            BN /= 2;
-    }
-
     CUtensorMap tmW, tmW2;
     int rc = make_tmap_2d_sw128(&tmW, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldw, kBK, BN);
     if (rc) return rc;

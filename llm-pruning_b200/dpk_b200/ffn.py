@@ -51,6 +51,8 @@ class RoutedFFN:
         self.row_bits = torch.empty((M, words), dtype=i32, device=dev)
         self.win_bits = torch.empty(((M + 127) // 128, words), dtype=i32, device=dev)
         self.h = torch.empty((M, I), dtype=gate_weight.dtype, device=dev)
+        self.acc_bytes = self.lib.dpk_gemm_k_workspace_bytes(M, H)
+        self.acc = torch.empty(max(self.acc_bytes, 16), dtype=u8, device=dev)
         self.launches_per_call = 3 + 1 + 1 + 1   # route (3 kernels), bits, gate/up, down
 
     def __call__(self, x: torch.Tensor, mask: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -100,7 +102,8 @@ class RoutedFFN:
             ck(lib.dpk_gemm_k(self.h.data_ptr() + r0 * I * esz, I, self.wd.data_ptr(), I,
                               self.row_bits.data_ptr() + r0 * words * 4,
                               self.win_bits.data_ptr() + (r0 // 128) * words * 4,
-                              y.data_ptr() + r0 * H * esz, H, rows, H, I, NG, self.code, st))
+                              y.data_ptr() + r0 * H * esz, H, rows, H, I, NG, self.code,
+                              self.acc.data_ptr() if self.acc_bytes else None, self.acc_bytes, st))
             if chunk_done is not None:
                 chunk_done(y[r0:r0 + rows])
         if ev is not None:

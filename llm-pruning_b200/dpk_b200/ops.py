@@ -259,9 +259,11 @@ def gemm_k(A: torch.Tensor, B: torch.Tensor, Mask: torch.Tensor, D: Optional[tor
             win_bits = torch.empty(((M + 127) // 128, words), dtype=torch.int32, device=dev)
             N.check(lib.dpk_mask_pack(m8.data_ptr(), M, NG, row_bits.data_ptr(),
                                       win_bits.data_ptr(), _stream()))
+            nbytes = lib.dpk_gemm_k_workspace_bytes(M, Nw)
+            ws = torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
             N.check(lib.dpk_gemm_k(A_f.data_ptr(), A_f.stride(0), Bc.data_ptr(), Bc.stride(0),
                                    row_bits.data_ptr(), win_bits.data_ptr(), D2.data_ptr(),
-                                   D2.stride(0), M, Nw, K, NG, code, _stream()))
+                                   D2.stride(0), M, Nw, K, NG, code, _ptr(ws), nbytes, _stream()))
         if not use_gemv:
             smask, sidx, _ = _layout_for(Mask, sorted_mask, sorted_indices, (M, NG))
             metadata = dict(sorted_mask=smask, sorted_indices=sidx)

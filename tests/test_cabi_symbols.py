@@ -52,10 +52,10 @@ def test_argument_checks_reject_before_any_launch(lib):
     rc = lib.dpk_gemm_mn(p, 128, p, None, 128, p, p, p, 250, 8, 250, 128, 4, N.BF16, 0, None)
     assert rc == N.ERR_INVALID and "divisible" in N.last_error()
     # group width that the tensor-core path does not take
-    rc = lib.dpk_gemm_k(p, 96, p, 96, p, p, p, 64, 8, 64, 96, 2, N.BF16, None)
+    rc = lib.dpk_gemm_k(p, 96, p, 96, p, p, p, 64, 8, 64, 96, 2, N.BF16, None, 0, None)
     assert rc == N.ERR_INVALID and "multiple of 64" in N.last_error()
     # unknown dtype
-    rc = lib.dpk_gemm_k(p, 128, p, 128, p, p, p, 64, 8, 64, 128, 2, 7, None)
+    rc = lib.dpk_gemm_k(p, 128, p, 128, p, p, p, 64, 8, 64, 128, 2, 7, None, 0, None)
     assert rc == N.ERR_INVALID
     # head_dim outside {64,128}
     rc = lib.dpk_attn_prefill(p, p, p, p, p, None, p, 1, 16, 16, 4, 2, 96, 2, 0.1, 1, 0, N.BF16, None)
@@ -70,6 +70,8 @@ def test_workspace_sizes(lib):
     assert lib.dpk_route_workspace_bytes(2, 100, 8) == 2 * 1 * 8 * 4
     assert lib.dpk_ffn_workspace_bytes(8192, 4096, 14336, 112) > 8192 * 14336 * 2
     assert lib.dpk_attn_decode_workspace_bytes(64, 32768, 32, 8, 128, 8) == 64 * 32 * 32 * 130 * 4
+    assert lib.dpk_gemm_k_workspace_bytes(64, 4096) == 64 * 4096 * 4
+    assert lib.dpk_gemm_k_workspace_bytes(8192, 4096) == 0
 
 
 def test_ops_refuse_cpu_tensors():

@@ -546,3 +546,20 @@ def test_prefill_cross_length(ops):
     assert_rel_rows(out, O.attention_prefill(q, k, v, mask, leftpad=lp))
     out, _ = ops.attention_prefill(dev(q, bf), dev(k, bf), dev(v, bf), dev(mask), is_causal=False)
     assert_rel_rows(out, O.attention_prefill(q, k, v, mask, is_causal=False))
+
+
+@pytest.mark.parametrize("M,K,N,NG", [(64, 14336, 4096, 112), (7, 512, 256, 4), (130, 1024, 512, 8),
+                                      (512, 2048, 256, 16)])
+def test_gemm_k_decode_sizes_split_accumulation(ops, M, K, N, NG):
+    """Few token windows: the group range is split over CTAs and summed in fp32."""
+    bf = torch.bfloat16
+    g = seeded(M + N)
+    a = bf16r(torch.randn(1, M, K, generator=g))
+    w = bf16r(torch.randn(N, K, generator=g) / K ** 0.5)
+    mask = torch.rand(1, M, NG, generator=g) > 0.5
+    if M >= 130:
+        mask[0, 128:] = False          # a window with no active group at all
+    got, _ = ops.gemm_k(dev(a, bf), dev(w, bf), dev(mask))
+    want = O.gemm_k(a, w, mask)
+    assert_rel_active(got, want)
+    assert torch.all(got.float().cpu()[want == 0] == 0)
