@@ -135,6 +135,15 @@ int dpk_route_counts(const uint8_t* sorted_mask, int batches, int64_t M, int NG,
 int dpk_mask_pack(const uint8_t* mask, int64_t M, int NG, uint32_t* row_bits, uint32_t* win_bits,
                   void* stream);
 
+/*
+ * dpk_route_compact (batches = 1) and dpk_mask_pack in one pass over the mask: everything
+ * the fused FFN needs from the routing decision, in three launches.  Same outputs, same
+ * workspace as dpk_route_compact.
+ */
+int dpk_route_plan(const uint8_t* mask, int64_t M, int NG, uint8_t* sorted_mask,
+                   int64_t* sorted_indices, int32_t* counts, uint32_t* row_bits, uint32_t* win_bits,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------ routed GEMMs ---- */
 
 /*

@@ -60,10 +60,8 @@ int dpk_ffn_swiglu(const void* x, const void* Wg, const void* Wu, const void* Wd
     uint32_t* win_bits = reinterpret_cast<uint32_t*>(ws + L.win_bits);
     void* h = ws + L.h;
 
-    int rc = dpk_route_compact(mask, 1, M, NG, smask, sidx, counts, ws + L.route_ws,
-                               up256(dpk_route_workspace_bytes(1, M, NG)), stream);
-    if (rc) return rc;
-    rc = dpk_mask_pack(mask, M, NG, row_bits, win_bits, stream);
+    int rc = dpk_route_plan(mask, M, NG, smask, sidx, counts, row_bits, win_bits, ws + L.route_ws,
+                            up256(dpk_route_workspace_bytes(1, M, NG)), stream);
     if (rc) return rc;
     // h[t, g-block] = silu(x Wg^T) * (x Wu^T) for active (t, g); other blocks are left as
     // they are and never read: the down projection zeroes them on the fly.

@@ -30,12 +30,16 @@ __device__ __forceinline__ void route_load_tile(const uint8_t* __restrict__ mask
     }
 }
 
-// pass 1: active rows of every (row block, column)
+// pass 1: active rows of every (row block, column); optionally also the packed routing
+// bits of the reduction-width GEMM (row_bits / win_bits, see mask_pack_kernel), which come
+// for free from the tile that is already in shared memory
 __global__ void __launch_bounds__(kRouteThreads)
 route_count_kernel(const uint8_t* __restrict__ mask, int64_t M, int NG, int nrb,
-                   int32_t* __restrict__ block_cnt)
+                   int32_t* __restrict__ block_cnt, uint32_t* __restrict__ row_bits,
+                   uint32_t* __restrict__ win_bits, int words)
 {
     __shared__ uint8_t tile[kRouteRows][kRouteCols + 4];
+    __shared__ uint32_t win_or[kRouteThreads / 32];
     const int b = blockIdx.z;
     const int rb = blockIdx.x;
     const int c0 = blockIdx.y * kRouteCols;
@@ -54,9 +58,33 @@ route_count_kernel(const uint8_t* __restrict__ mask, int64_t M, int NG, int nrb,
         }
         if (lane == 0) block_cnt[(static_cast<int64_t>(b) * nrb + rb) * NG + c] = total;
     }
+    if (row_bits != nullptr) {
+        // warp w packs rows [32w, 32w+32) of the tile: one word (this column block) per row
+        uint32_t acc = 0;
+        for (int i = 0; i < 32; ++i) {
+            const int row = warp * 32 + i;
+            const uint32_t bits = __ballot_sync(0xffffffffu, tile[row][lane] != 0);
+            acc |= bits;
+            const int64_t r = r0 + row;
+            if (lane == 0 && r < M) row_bits[r * words + blockIdx.y] = bits;
+        }
+        if (lane == 0) win_or[warp] = acc;
+        __syncthreads();
+        // the tile covers two 128-row windows: warps 0-3 and warps 4-7
+        if (threadIdx.x < 2) {
+            const int64_t win = static_cast<int64_t>(rb) * 2 + threadIdx.x;
+            if (win * 128 < M) {
+                const int w0 = threadIdx.x * 4;
+                win_bits[win * words + blockIdx.y] =
+                    win_or[w0] | win_or[w0 + 1] | win_or[w0 + 2] | win_or[w0 + 3];
+            }
+        }
+    }
 }
 
-// pass 2: exclusive scan over row blocks per column (in place), totals into counts
+// pass 2: exclusive scan over row blocks per column (in place), totals into counts.
+// The counters of 16 row blocks are fetched with independent loads before any is
+// rewritten, so the latency of the column walk is paid once per 16 blocks.
 __global__ void route_scan_kernel(int32_t* __restrict__ block_cnt, int nrb, int NG, int batches,
                                   int32_t* __restrict__ counts)
 {
@@ -65,10 +93,16 @@ __global__ void route_scan_kernel(int32_t* __restrict__ block_cnt, int nrb, int 
     int b = i / NG, c = i % NG;
     int32_t run = 0;
     int32_t* p = block_cnt + static_cast<int64_t>(b) * nrb * NG + c;
-    for (int rb = 0; rb < nrb; ++rb) {
-        int32_t v = p[static_cast<int64_t>(rb) * NG];
-        p[static_cast<int64_t>(rb) * NG] = run;
-        run += v;
+    for (int rb0 = 0; rb0 < nrb; rb0 += 16) {
+        int32_t v[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+            v[k] = rb0 + k < nrb ? p[static_cast<int64_t>(rb0 + k) * NG] : 0;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            if (rb0 + k < nrb) p[static_cast<int64_t>(rb0 + k) * NG] = run;
+            run += v[k];
+        }
     }
     counts[i] = run;
 }
@@ -172,10 +206,71 @@ mask_pack_kernel(const uint8_t* __restrict__ mask, int64_t M, int NG, int words,
             s_or[w] | s_or[words + w] | s_or[2 * words + w] | s_or[3 * words + w];
 }
 
-// top-k mask: one warp per token row; rank by counting, ties to the lower index
+// top-k mask: one warp per token row.  The k-th largest logit is found by a bitwise binary
+// search over order-preserving integer keys (32 steps of count-and-compare), then
+// everything above it is kept and ties with it are kept in index order, so that ties go to
+// the lower group index.
+__device__ __forceinline__ uint32_t topk_key(float f)
+{
+    // monotone map float -> uint32 (larger float = larger key); -0 and +0 coincide
+    uint32_t u = __float_as_uint(f + 0.0f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+constexpr int kTopkPerLane = 8;    // covers NG <= 256 in registers
+
 __global__ void __launch_bounds__(128)
 topk_mask_kernel(const float* __restrict__ logits, int64_t M, int NG, int keep,
                  uint8_t* __restrict__ mask)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * 4 + warp;
+    if (r >= M) return;
+    uint32_t key[kTopkPerLane];
+#pragma unroll
+    for (int i = 0; i < kTopkPerLane; ++i) {
+        const int g = i * 32 + lane;
+        key[i] = g < NG ? topk_key(logits[r * NG + g]) : 0u;   // real keys are never 0
+    }
+    if (keep <= 0 || keep >= NG) {
+#pragma unroll
+        for (int i = 0; i < kTopkPerLane; ++i) {
+            const int g = i * 32 + lane;
+            if (g < NG) mask[r * NG + g] = keep > 0 ? 1 : 0;
+        }
+        return;
+    }
+    // largest T with count(key >= T) >= keep  ==  the keep-th largest key
+    uint32_t thr = 0;
+    for (int bit = 31; bit >= 0; --bit) {
+        const uint32_t cand = thr | (1u << bit);
+        int cnt = 0;
+#pragma unroll
+        for (int i = 0; i < kTopkPerLane; ++i) cnt += key[i] >= cand;
+        cnt = __reduce_add_sync(0xffffffffu, cnt);
+        if (cnt >= keep) thr = cand;
+    }
+    int above = 0;
+#pragma unroll
+    for (int i = 0; i < kTopkPerLane; ++i) above += key[i] > thr;
+    above = __reduce_add_sync(0xffffffffu, above);
+    int ties_left = keep - above;                     // ties to keep, lowest indices first
+    const unsigned lt = (1u << lane) - 1u;
+#pragma unroll
+    for (int i = 0; i < kTopkPerLane; ++i) {
+        const int g = i * 32 + lane;
+        const bool tie = g < NG && key[i] == thr;
+        const unsigned bal = __ballot_sync(0xffffffffu, tie);
+        const bool on = g < NG && (key[i] > thr || (tie && __popc(bal & lt) < ties_left));
+        if (g < NG) mask[r * NG + g] = on ? 1 : 0;
+        ties_left -= __popc(bal);
+    }
+}
+
+// same result for any NG (rank by counting through shared memory); used beyond 256 groups
+__global__ void __launch_bounds__(128)
+topk_mask_rank_kernel(const float* __restrict__ logits, int64_t M, int NG, int keep,
+                      uint8_t* __restrict__ mask)
 {
     extern __shared__ float s_l[];   // [4][NG]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -239,8 +334,12 @@ int dpk_topk_mask(const float* logits, int64_t M, int NG, int keep, uint8_t* mas
     DPK_REQUIRE(keep >= 0 && keep <= NG, "keep=%d outside [0,%d]", keep, NG);
     if (M == 0) return DPK_OK;
     unsigned blocks = static_cast<unsigned>((M + 3) / 4);
-    topk_mask_kernel<<<blocks, 128, 4 * NG * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
-        logits, M, NG, keep, mask);
+    if (NG <= 32 * kTopkPerLane)
+        topk_mask_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, M, NG, keep,
+                                                                               mask);
+    else
+        topk_mask_rank_kernel<<<blocks, 128, 4 * NG * sizeof(float),
+                                static_cast<cudaStream_t>(stream)>>>(logits, M, NG, keep, mask);
     DPK_CUDA(cudaGetLastError());
     return DPK_OK;
 }
@@ -274,7 +373,7 @@ int dpk_route_compact(const uint8_t* mask, int batches, int64_t M, int NG, uint8
     DPK_REQUIRE(ncb <= 65535, "NG=%d too large", NG);
     int32_t* block_cnt = static_cast<int32_t*>(workspace);
     dim3 grid(nrb, ncb, batches);
-    route_count_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt);
+    route_count_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt, nullptr, nullptr, 0);
     int total = batches * NG;
     route_scan_kernel<<<(total + 127) / 128, 128, 0, s>>>(block_cnt, nrb, NG, batches, counts);
     route_scatter_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt, counts,
@@ -337,9 +436,37 @@ int dpk_route_compact_static(const uint8_t* mask, int batches, int64_t M, int NG
     dim3 grid(nrb, ncb, batches);
     // every counter this call reads is written by the first kernel, so nothing left by an
     // earlier call needs clearing
-    route_count_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt);
+    route_count_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt, nullptr, nullptr, 0);
     int total = batches * NG;
     route_scan_kernel<<<(total + 127) / 128, 128, 0, s>>>(block_cnt, nrb, NG, batches, counts);
+    route_scatter_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt, counts,
+                                                         sorted_mask, sorted_indices);
+    DPK_CUDA(cudaGetLastError());
+    return DPK_OK;
+}
+
+int dpk_route_plan(const uint8_t* mask, int64_t M, int NG, uint8_t* sorted_mask,
+                   int64_t* sorted_indices, int32_t* counts, uint32_t* row_bits, uint32_t* win_bits,
+                   void* workspace, size_t workspace_bytes, void* stream)
+{
+    DPK_REQUIRE(mask && sorted_mask && sorted_indices && counts && row_bits && win_bits, "NULL tensor");
+    DPK_REQUIRE(M >= 0 && M < (1ll << 31) && NG >= 1 && NG <= 8192, "bad shape M=%lld NG=%d",
+                (long long)M, NG);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (M == 0) {
+        DPK_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * NG, s));
+        return DPK_OK;
+    }
+    size_t need = dpk_route_workspace_bytes(1, M, NG);
+    DPK_REQUIRE(workspace && workspace_bytes >= need, "workspace of %zu bytes needed, %zu given",
+                need, workspace_bytes);
+    int nrb = static_cast<int>((M + kRouteRows - 1) / kRouteRows);
+    int ncb = (NG + kRouteCols - 1) / kRouteCols;     // == words of the packed bits
+    int32_t* block_cnt = static_cast<int32_t*>(workspace);
+    dim3 grid(nrb, ncb, 1);
+    route_count_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt, row_bits, win_bits,
+                                                       ncb);
+    route_scan_kernel<<<(NG + 127) / 128, 128, 0, s>>>(block_cnt, nrb, NG, 1, counts);
     route_scatter_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt, counts,
                                                          sorted_mask, sorted_indices);
     DPK_CUDA(cudaGetLastError());

@@ -31,6 +31,7 @@ SIGNATURES = {
     "dpk_route_compact_static": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _vp]),
     "dpk_route_counts": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp]),
     "dpk_mask_pack": (_i32, [_vp, _i64, _i32, _vp, _vp, _vp]),
+    "dpk_route_plan": (_i32, [_vp, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "dpk_gemm_mn": (_i32, [_vp, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32,
                            _i32, _i32, _vp]),
     "dpk_gemm_k": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32,

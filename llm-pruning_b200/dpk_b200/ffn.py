@@ -53,7 +53,7 @@ class RoutedFFN:
         self.h = torch.empty((M, I), dtype=gate_weight.dtype, device=dev)
         self.acc_bytes = self.lib.dpk_gemm_k_workspace_bytes(M, H)
         self.acc = torch.empty(max(self.acc_bytes, 16), dtype=u8, device=dev)
-        self.launches_per_call = 3 + 1 + 1 + 1   # route (3 kernels), bits, gate/up, down
+        self.launches_per_call = 3 + 1 + 1       # routing plan (3 kernels), gate/up, down
 
     def __call__(self, x: torch.Tensor, mask: torch.Tensor, out: Optional[torch.Tensor] = None,
                  events: Optional[Dict[str, List[Tuple[torch.cuda.Event, torch.cuda.Event]]]] = None,
@@ -79,11 +79,10 @@ class RoutedFFN:
             (M, self.H), dtype=xf.dtype, device=self.device)
         lib, st, ck = self.lib, _stream(), N.check
         H, I, NG = self.H, self.I, self.NG
-        ck(lib.dpk_route_compact(m8.data_ptr(), 1, M, NG, self.sorted_mask.data_ptr(),
-                                 self.sorted_indices.data_ptr(), self.counts.data_ptr(),
-                                 self.route_ws.data_ptr(), self.route_ws_bytes, st))
-        ck(lib.dpk_mask_pack(m8.data_ptr(), M, NG, self.row_bits.data_ptr(),
-                             self.win_bits.data_ptr(), st))
+        ck(lib.dpk_route_plan(m8.data_ptr(), M, NG, self.sorted_mask.data_ptr(),
+                              self.sorted_indices.data_ptr(), self.counts.data_ptr(),
+                              self.row_bits.data_ptr(), self.win_bits.data_ptr(),
+                              self.route_ws.data_ptr(), self.route_ws_bytes, st))
         ev = None
         if events is not None:
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]

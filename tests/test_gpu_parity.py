@@ -563,3 +563,43 @@ def test_gemm_k_decode_sizes_split_accumulation(ops, M, K, N, NG):
     want = O.gemm_k(a, w, mask)
     assert_rel_active(got, want)
     assert torch.all(got.float().cpu()[want == 0] == 0)
+
+
+def test_topk_wide_and_edge_keeps(ops):
+    g = seeded(41)
+    for M, NG, keep in ((50, 300, 17), (33, 256, 255), (20, 40, 40), (20, 40, 0), (9, 1, 1)):
+        logits = torch.randn(M, NG, generator=g)
+        logits[0, : min(NG, 7)] = 1.25                      # a run of ties
+        got = ops.topk_route_mask(dev(logits), keep).cpu()
+        assert torch.equal(got, O.topk_route_mask(logits, keep)), (M, NG, keep)
+        assert np.array_equal(got.numpy(), RO.topk_mask(logits.numpy(), keep))
+    neg = -torch.rand(64, 112, generator=g)                 # negative logits and signed zeros
+    neg[:, 5] = -0.0
+    neg[:, 9] = 0.0
+    assert torch.equal(ops.topk_route_mask(dev(neg), 56).cpu(), O.topk_route_mask(neg, 56))
+
+
+def test_route_plan_matches_separate_calls(ops):
+    from dpk_b200 import _native as N
+    lib = N.load()
+    st = torch.cuda.current_stream().cuda_stream
+    for M, NG in ((8192, 112), (300, 40), (129, 224), (64, 8)):
+        mask = torch.rand(M, NG, generator=seeded(M)) > 0.5
+        m8 = dev(mask).view(torch.uint8)
+        words, nwin = (NG + 31) // 32, (M + 127) // 128
+        smask = torch.empty_like(m8)
+        sidx = torch.empty((M, NG), dtype=torch.int64, device="cuda")
+        counts = torch.empty(NG, dtype=torch.int32, device="cuda")
+        rb = torch.full((M, words), -1, dtype=torch.int32, device="cuda")
+        wb = torch.full((nwin, words), -1, dtype=torch.int32, device="cuda")
+        nbytes = lib.dpk_route_workspace_bytes(1, M, NG)
+        ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+        N.check(lib.dpk_route_plan(m8.data_ptr(), M, NG, smask.data_ptr(), sidx.data_ptr(),
+                                   counts.data_ptr(), rb.data_ptr(), wb.data_ptr(), ws.data_ptr(),
+                                   nbytes, st))
+        es, ei = torch.sort(mask, dim=0, descending=True, stable=True)
+        assert torch.equal(sidx.cpu(), ei) and torch.equal(smask.cpu().view(torch.bool), es)
+        assert torch.equal(counts.cpu(), mask.sum(0).to(torch.int32))
+        erb, ewb = RO.row_bits(mask.numpy(), 128)
+        assert np.array_equal(rb.cpu().numpy().view(np.uint32), erb)
+        assert np.array_equal(wb.cpu().numpy().view(np.uint32), ewb)
