@@ -119,7 +119,8 @@ int dpk_route_compact_static(const uint8_t* mask, int batches, int64_t M, int NG
                              void* stream);
 
 /*
- * counts[b,g] = number of non-zero entries of column g of sorted_mask [batches,M,NG].  Used
+ * counts[b,g] = number of leading non-zero entries of column g of sorted_mask
+ * [batches,M,NG] (every active row of a column precedes every inactive one).  Used
  * when the caller passes `sorted_mask` / `sorted_indices` from an earlier call
  * (metadata reuse, DynamicPruningKernels/tests/test_gpu_smoke.py:203-292).
  */

@@ -49,6 +49,8 @@ struct MnParams {
     int fused;              // second weight present: silu(gate)*up
     int act;
     int rows_per_block;     // row tiles of one group scheduled back to back (L2 blocking of A)
+    int halves;             // 128-row halves per tile: 2 when two accumulators of <= 128 columns
+                            // fit, so that one weight tile feeds 256 token rows
     int stages;             // ring depth: kRingBytes / stage_bytes, at most kMaxStages
     int stage_bytes;        // kAStageBytes + (UMMA N) * 128
     int* status;
@@ -124,6 +126,9 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int KB = (p.K + kBK - 1) / kBK;
     const int nst = p.stages;
     const int stage_bytes = p.stage_bytes;
+    const int halves = p.halves;
+    const int RT = kBM * halves;              // token rows per tile
+    const int a_bytes = kAStageBytes * halves;
 
     // ---- set-up --------------------------------------------------------------------
     if (warp == 0) {
@@ -132,7 +137,7 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         for (int g = lane; g < p.NG; g += 32) {
             int c = p.counts[g];
             c = c < 0 ? 0 : c;
-            tmin = min(tmin, (c + kBM - 1) / kBM);
+            tmin = min(tmin, (c + RT - 1) / RT);
         }
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) tmin = min(tmin, __shfl_xor_sync(0xffffffffu, tmin, d));
@@ -144,7 +149,7 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if (g < p.NG) {
                 int c = p.counts[g];
                 c = c < 0 ? 0 : c;
-                v = ((c + kBM - 1) / kBM - tmin) * p.n_chunks;
+                v = ((c + RT - 1) / RT - tmin) * p.n_chunks;
             }
             int incl = v;
 #pragma unroll
@@ -198,7 +203,14 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             int g, mtile, nchunk;
             tmap.decode(tile, g, mtile, nchunk);
             const int cnt = p.counts[g];
-            const int slot = mtile * kBM + warp * 32 + lane;
+            const int ab = acc_it & 1;
+            // the TMEM loads below are warp-collective: leave only as a whole warp
+            const bool got = mbar_wait(&tfull[ab], (acc_it >> 1) & 1, abort_flag, p.status,
+                                       DPK_DEV_TIMEOUT_TMEM_FULL);
+            if (!__all_sync(0xffffffffu, got)) break;
+            tc_fence_after_sync();
+            for (int half = 0; half < halves; ++half) {
+            const int slot = mtile * RT + half * kBM + warp * 32 + lane;
             bool valid = slot < cnt;
             int64_t tok = 0;
             if (valid) {
@@ -208,14 +220,8 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     valid = false;
                 }
             }
-            const int ab = acc_it & 1;
-            // the TMEM loads below are warp-collective: leave only as a whole warp
-            const bool got = mbar_wait(&tfull[ab], (acc_it >> 1) & 1, abort_flag, p.status,
-                                       DPK_DEV_TIMEOUT_TMEM_FULL);
-            if (!__all_sync(0xffffffffu, got)) break;
-            tc_fence_after_sync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) +
-                                   static_cast<uint32_t>(ab * 256);
+                                   static_cast<uint32_t>(ab * 256 + half * 128);
             uint8_t* out = p.D + (tok * p.ldd + static_cast<int64_t>(g) * p.G +
                                   static_cast<int64_t>(nchunk) * BN) * 2;
             if (p.fused) {
@@ -283,6 +289,7 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     }
                 }
             }
+            }   // halves
             tc_fence_before_sync();
             mbar_arrive(&tempty[ab]);
         }
@@ -302,7 +309,7 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                         ok = false;
                         break;
                     }
-                    uint8_t* sb = smem + size_t(s) * stage_bytes + kAStageBytes;
+                    uint8_t* sb = smem + size_t(s) * stage_bytes + a_bytes;
                     mbar_arrive_expect_tx(&full[s], tx_bytes);
                     tma_load_2d(sb, &tmW, &full[s], kb * kBK, row0);
                     if (p.fused) tma_load_2d(sb + BN * kBK * 2, &tmW2, &full[s], kb * kBK, row0);
@@ -331,13 +338,15 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     }
                     tc_fence_after_sync();
                     const uint32_t sa = smem_u32(smem + size_t(s) * stage_bytes);
-                    const uint64_t adesc = umma_desc_k_sw128(sa);
-                    const uint64_t bdesc = umma_desc_k_sw128(sa + kAStageBytes);
+                    const uint64_t bdesc = umma_desc_k_sw128(sa + a_bytes);
+                    for (int half = 0; half < halves; ++half) {
+                        const uint64_t adesc = umma_desc_k_sw128(sa + half * kAStageBytes);
 #pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k) {
-                        // 16 elements = 32 bytes further along K inside the swizzle atom
-                        umma_f16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc,
-                                    (kb | k) != 0 ? 1u : 0u);
+                        for (int k = 0; k < kBK / 16; ++k) {
+                            // 16 elements = 32 bytes further along K inside the swizzle atom
+                            umma_f16_ss(d_tmem + half * 128, adesc + 2 * k, bdesc + 2 * k, idesc,
+                                        (kb | k) != 0 ? 1u : 0u);
+                        }
                     }
                     umma_commit(&empty[s]);
                     if (++s == nst) { s = 0; ph ^= 1; }
@@ -360,12 +369,12 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             int g, mtile, nchunk;
             tmap.decode(tile, g, mtile, nchunk);
             const int cnt = p.counts[g];
-            const uint8_t* src_row[8];
+            const uint8_t* src_row[16];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int slot = mtile * kBM + i * 16 + rsub;
+            for (int i = 0; i < 16; ++i) {
+                const int slot = mtile * RT + i * 16 + rsub;
                 src_row[i] = nullptr;
-                if (slot < cnt) {
+                if (i < 8 * halves && slot < cnt) {
                     int64_t tok = p.sidx[static_cast<int64_t>(slot) * p.NG + g];
                     if (tok >= 0 && tok < p.M) src_row[i] = p.A + tok * p.lda * 2;
                 }
@@ -379,11 +388,13 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 const bool kvalid = kcol < p.K;
                 const uint32_t dst = smem_u32(smem + size_t(s) * stage_bytes) + dst_off;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const bool on = kvalid && src_row[i] != nullptr;
-                    const void* src = on ? static_cast<const void*>(src_row[i] + kcol * 2)
-                                         : static_cast<const void*>(p.A);
-                    cp_async_16(dst + i * 16 * 128, src, on ? 16u : 0u);
+                for (int i = 0; i < 16; ++i) {
+                    if (i < 8 * halves) {
+                        const bool on = kvalid && src_row[i] != nullptr;
+                        const void* src = on ? static_cast<const void*>(src_row[i] + kcol * 2)
+                                             : static_cast<const void*>(p.A);
+                        cp_async_16(dst + i * 16 * 128, src, on ? 16u : 0u);
+                    }
                 }
                 cp_async_commit();
                 if (++s == nst) { s = 0; ph ^= 1; }
@@ -472,21 +483,25 @@ extern "C" int dpk_gemm_mn(const void* A, int64_t lda, const void* W, const void
     p.n_chunks = G / BN;
     p.fused = fused;
     p.act = act;
+    const int umma_n = fused ? 2 * BN : BN;
+    // Two accumulators of <= 128 columns fit next to their double buffers in TMEM: let one
+    // weight tile feed 256 token rows, which halves the weight bytes per flop.
+    p.halves = (umma_n <= 128 && M >= 1024) ? 2 : 1;
     {
-        // a block of R row tiles spans about 2*128*R token rows at a 50 % keep ratio; keep the
+        // a block of R row tiles spans about 2*rows*R token rows at a 50 % keep ratio; keep the
         // rows it gathers (K*2 bytes each) within ~48 MiB so that they stay in L2
         const int64_t span_rows = (48ll << 20) / (static_cast<int64_t>(K) * 2);
-        int r = static_cast<int>(span_rows / (2 * kBM));
+        int r = static_cast<int>(span_rows / (2 * kBM * p.halves));
         p.rows_per_block = r < 4 ? 4 : (r > 4096 ? 4096 : r);
     }
-    p.stage_bytes = kAStageBytes + (fused ? 2 * BN : BN) * kBK * 2;
+    p.stage_bytes = kAStageBytes * p.halves + umma_n * kBK * 2;
     p.stages = kRingBytes / p.stage_bytes;
     if (p.stages > kMaxStages) p.stages = kMaxStages;
     p.status = device_status_ptr();
     if (!p.status) return fail(DPK_ERR_CUDA, "no status word on this device");
 
     // upper bound of the tile count, known without reading counts[] back
-    int64_t bound = ((M + kBM - 1) / kBM + 1) * (int64_t)NG * p.n_chunks;
+    int64_t bound = ((M + kBM * p.halves - 1) / (kBM * p.halves) + 1) * (int64_t)NG * p.n_chunks;
     int grid = sm_count();
     if (bound < grid) grid = (int)bound;
     if (grid < 1) grid = 1;

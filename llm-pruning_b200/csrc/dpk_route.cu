@@ -158,26 +158,24 @@ route_scatter_kernel(const uint8_t* __restrict__ mask, int64_t M, int NG, int nr
     }
 }
 
-// counts of a caller-supplied sorted_mask
-__global__ void __launch_bounds__(256)
+// counts of a caller-supplied sorted_mask.  The layout puts every active row of a column
+// before every inactive one (the invariant the reference's kernels rely on as well,
+// include/gemm_mn/v1/sm12x.cuh:272-311), so the count is the position of the first zero:
+// one thread per column, a binary search of log2(M) loads.
+__global__ void __launch_bounds__(128)
 route_counts_kernel(const uint8_t* __restrict__ sorted_mask, int64_t M, int NG,
                     int32_t* __restrict__ counts)
 {
-    __shared__ int part[8][32];
     const int b = blockIdx.y;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int c = blockIdx.x * 32 + lane;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= NG) return;
     sorted_mask += static_cast<int64_t>(b) * M * NG;
-    int total = 0;
-    if (c < NG)
-        for (int64_t r = warp; r < M; r += 8) total += sorted_mask[r * NG + c] != 0;
-    part[warp][lane] = total;
-    __syncthreads();
-    if (warp == 0 && c < NG) {
-        int s = 0;
-        for (int w = 0; w < 8; ++w) s += part[w][lane];
-        counts[static_cast<int64_t>(b) * NG + c] = s;
+    int64_t lo = 0, hi = M;              // invariant: rows < lo are active, rows >= hi are not
+    while (lo < hi) {
+        const int64_t mid = (lo + hi) >> 1;
+        if (sorted_mask[mid * NG + c] != 0) lo = mid + 1; else hi = mid;
     }
+    counts[static_cast<int64_t>(b) * NG + c] = static_cast<int32_t>(lo);
 }
 
 // packed bits: one CTA per 128-row window
@@ -387,8 +385,8 @@ int dpk_route_counts(const uint8_t* sorted_mask, int batches, int64_t M, int NG,
 {
     DPK_REQUIRE(sorted_mask && counts, "NULL tensor");
     DPK_REQUIRE(batches >= 1 && batches <= 65535 && M >= 0 && NG >= 1, "bad shape");
-    dim3 grid((NG + 31) / 32, batches);
-    route_counts_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(sorted_mask, M, NG,
+    dim3 grid((NG + 127) / 128, batches);
+    route_counts_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(sorted_mask, M, NG,
                                                                               counts);
     DPK_CUDA(cudaGetLastError());
     return DPK_OK;

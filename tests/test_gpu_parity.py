@@ -603,3 +603,26 @@ def test_route_plan_matches_separate_calls(ops):
         erb, ewb = RO.row_bits(mask.numpy(), 128)
         assert np.array_equal(rb.cpu().numpy().view(np.uint32), erb)
         assert np.array_equal(wb.cpu().numpy().view(np.uint32), ewb)
+
+
+@pytest.mark.parametrize("M,K,N,NG,fused", [(2000, 256, 512, 4, False), (1500, 128, 256, 2, False),
+                                            (1030, 192, 256, 4, True), (4096, 512, 1024, 8, False)])
+def test_gemm_mn_double_row_tiles(ops, M, K, N, NG, fused):
+    """Narrow groups with many tokens use 256-row tiles (two accumulators per weight tile)."""
+    bf = torch.bfloat16
+    g = seeded(M + K)
+    a = bf16r(torch.randn(1, M, K, generator=g))
+    w = bf16r(torch.randn(N, K, generator=g) / K ** 0.5)
+    w2 = bf16r(torch.randn(N, K, generator=g) / K ** 0.5)
+    mask = torch.rand(1, M, NG, generator=g) > 0.5
+    mask[0, :, 0] = torch.arange(M) < 300          # a group whose list ends inside a first half
+    if fused:
+        got, _ = ops.gemm_mn(dev(a, bf), dev(w, bf), dev(mask), up_weight=dev(w2, bf))
+        want = O.gemm_mn(a, w, mask, "silu") * O.gemm_mn(a, w2, mask)
+        assert_ref_tol(got, want)
+        assert_rel_active(got, want, tol=4e-2)
+    else:
+        got, _ = ops.gemm_mn(dev(a, bf), dev(w, bf), dev(mask), activation="relu")
+        want = O.gemm_mn(a, w, mask, "relu")
+        assert_rel_active(got, want)
+    assert torch.all(got.float().cpu()[0][~mask[0].repeat_interleave(N // NG, dim=-1)] == 0)
