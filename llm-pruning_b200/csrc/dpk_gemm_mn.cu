@@ -21,88 +21,9 @@
 // tile i overlaps the main loop of tile i+1.
 //
 // Algorithmic work per launch: 2*K*G flops per active (token, group) pair per weight.
-#include "dpk_host.h"
-#include "dpk_sm100.cuh"
+#include "dpk_gemm_mn.cuh"
 
 namespace dpk {
-
-constexpr int kBM = 128;
-constexpr int kBK = 64;
-constexpr int kAStageBytes = kBM * kBK * 2;         // 16 KiB of gathered token rows
-constexpr int kRingBytes = 4 * (kAStageBytes + 256 * kBK * 2);   // 192 KiB of operand ring
-constexpr int kMaxStages = 12;
-constexpr int kMnThreads = 320;
-constexpr int kMaxGroups = 2048;
-constexpr int kGatherLag = 2;                       // cp.async groups kept in flight
-constexpr int kTmemCols = 512;
-
-struct MnParams {
-    const uint8_t* A;       // [M, lda] half
-    uint8_t* D;             // [M, ldd] half
-    const int64_t* sidx;    // [M, NG]
-    const int32_t* counts;  // [NG]
-    int64_t lda, ldd;       // elements
-    int64_t M;
-    int K, NG, G;
-    int BN;                 // output channels per tile and weight
-    int n_chunks;           // G / BN
-    int fused;              // second weight present: silu(gate)*up
-    int act;
-    int rows_per_block;     // row tiles of one group scheduled back to back (L2 blocking of A)
-    int halves;             // 128-row halves per tile: 2 when two accumulators of <= 128 columns
-                            // fit, so that one weight tile feeds 256 token rows
-    int stages;             // ring depth: kRingBytes / stage_bytes, at most kMaxStages
-    int stage_bytes;        // kAStageBytes + (UMMA N) * 128
-    int* status;
-};
-
-constexpr size_t kMnSmemBytes = 1024 /*alignment slack*/ + size_t(kRingBytes) +
-                                (2 * kMaxStages + 4) * sizeof(uint64_t) + 16 +
-                                (kMaxGroups + 1) * sizeof(int);
-
-__device__ __forceinline__ float apply_act(float x, int act)
-{
-    if (act == DPK_ACT_RELU) return fmaxf(x, 0.f);
-    if (act == DPK_ACT_SILU) return silu_f(x);
-    return x;
-}
-
-// Tile order.  Row tile i of every group covers roughly the same token range (the routing
-// keeps a similar fraction of every stretch of tokens), so the schedule walks blocks of R row
-// tiles and, inside a block, the groups: the token rows a block gathers stay L2-resident
-// while all groups use them, and one group's weight slab is shared by the R*n_chunks tiles
-// that run back to back.  Row tiles up to the smallest group's count form this regular part
-// (decoded arithmetically); the few tiles beyond it are appended group by group.
-struct TileMap {
-    const int* ragged_prefix;   // [NG + 1] tiles of group g beyond the regular part
-    int ng, n_chunks, rows_per_block, tmin, regular_total, total;
-
-    __device__ __forceinline__ void decode(int tile, int& g, int& mtile, int& nchunk) const
-    {
-        if (tile < regular_total) {
-            const int per_block = rows_per_block * ng * n_chunks;
-            const int mb = tile / per_block;
-            const int off = tile - mb * per_block;
-            const int rows = min(rows_per_block, tmin - mb * rows_per_block);
-            const int per_group = rows * n_chunks;
-            g = off / per_group;
-            const int rem = off - g * per_group;
-            mtile = mb * rows_per_block + rem / n_chunks;
-            nchunk = rem % n_chunks;
-        } else {
-            const int u0 = tile - regular_total;
-            int lo = 0, hi = ng;   // invariant: ragged_prefix[lo] <= u0 < ragged_prefix[hi]
-            while (hi - lo > 1) {
-                const int mid = (lo + hi) >> 1;
-                if (ragged_prefix[mid] <= u0) lo = mid; else hi = mid;
-            }
-            g = lo;
-            const int u = u0 - ragged_prefix[g];
-            mtile = tmin + u / n_chunks;
-            nchunk = u % n_chunks;
-        }
-    }
-};
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kMnThreads, 1)
@@ -507,6 +428,23 @@ extern "C" int dpk_gemm_mn(const void* A, int64_t lda, const void* W, const void
     if (grid < 1) grid = 1;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    {
+        // wide tiles with many tokens: CTA pairs (tcgen05 cta_group::2) share each weight tile
+        if (umma_n == 256 && M >= 2048 && sm_count() >= 2) {
+            CUtensorMap pw, pw2;
+            rc = make_tmap_2d_sw128(&pw, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldw, kBK, 128);
+            if (rc) return rc;
+            rc = make_tmap_2d_sw128(&pw2, fused ? W2 : W, (uint64_t)K, (uint64_t)N, (uint64_t)ldw, kBK,
+                                    128);
+            if (rc) return rc;
+            MnParams q = p;
+            q.halves = 2;
+            const int64_t span_rows = (48ll << 20) / (static_cast<int64_t>(K) * 2);
+            int r = static_cast<int>(span_rows / (4 * kBM));
+            q.rows_per_block = r < 4 ? 4 : (r > 4096 ? 4096 : r);
+            return gemm_mn_pair_launch(pw, pw2, q, dtype, s);
+        }
+    }
     if (dtype == DPK_BF16) {
         DPK_CUDA(cudaFuncSetAttribute(gemm_mn_kernel<true>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMnSmemBytes));

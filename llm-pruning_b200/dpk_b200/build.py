@@ -27,6 +27,7 @@ SOURCES = [
     "dpk_host.cu",
     "dpk_route.cu",
     "dpk_gemm_mn.cu",
+    "dpk_gemm_mn_pair.cu",
     "dpk_gemm_k.cu",
     "dpk_gemv.cu",
     "dpk_ffn.cu",

@@ -626,3 +626,32 @@ def test_gemm_mn_double_row_tiles(ops, M, K, N, NG, fused):
         want = O.gemm_mn(a, w, mask, "relu")
         assert_rel_active(got, want)
     assert torch.all(got.float().cpu()[0][~mask[0].repeat_interleave(N // NG, dim=-1)] == 0)
+
+
+@pytest.mark.parametrize("M,K,N,NG,fused,dtype", [
+    (2100, 200, 512, 2, False, torch.bfloat16),     # G = 256: one 256-wide chunk per group, K tail
+    (4096, 512, 2048, 2, False, torch.float16),     # G = 1024: four chunks
+    (2500, 256, 512, 4, True, torch.bfloat16),      # gate/up pair, G = 128
+    (3000, 128, 256, 2, True, torch.float16),
+])
+def test_gemm_mn_cta_pairs(ops, M, K, N, NG, fused, dtype):
+    """Wide tiles with many tokens run on CTA pairs (one weight tile shared by two SMs)."""
+    g = seeded(M + N)
+    a = torch.randn(1, M, K, generator=g).to(dtype)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(dtype)
+    w2 = (torch.randn(N, K, generator=g) / K ** 0.5).to(dtype)
+    mask = torch.rand(1, M, NG, generator=g) > 0.5
+    mask[0, :, 0] = torch.arange(M) < 130           # a group that ends inside the second CTA's rows
+    if fused:
+        got, _ = ops.gemm_mn(dev(a), dev(w), dev(mask), up_weight=dev(w2))
+        want = O.gemm_mn(a.float(), w.float(), mask, "silu") * O.gemm_mn(a.float(), w2.float(), mask)
+        # a product of two Gaussians: its largest entries sit > 10 rms out, where half a
+        # 16-bit ulp alone is 5e-2 rms; the element-wise reference tolerance is the real check
+        assert_ref_tol(got, want)
+        assert_rel_active(got, want, tol=8e-2)
+    else:
+        got, _ = ops.gemm_mn(dev(a), dev(w), dev(mask))
+        want = O.gemm_mn(a.float(), w.float(), mask)
+        assert_rel_active(got, want)
+        assert_ref_tol(got, want)
+    assert torch.all(got.float().cpu()[0][~mask[0].repeat_interleave(N // NG, dim=-1)] == 0)
