@@ -20,40 +20,9 @@
 //
 // Algorithmic work per launch: 2*N*G flops per active (token, group) pair; executed
 // work: 2*N*G*128 per visited (window, group) block.
-#include "dpk_host.h"
-#include "dpk_sm100.cuh"
+#include "dpk_gemm_k.cuh"
 
 namespace dpk {
-
-constexpr int kBM = 128;
-constexpr int kBK = 64;
-constexpr int kAStageBytes = kBM * kBK * 2;
-constexpr int kRingBytes = 4 * (kAStageBytes + 256 * kBK * 2);   // 192 KiB of operand ring
-constexpr int kMaxStages = 12;
-constexpr int kKThreads = 320;
-constexpr int kTmemCols = 512;
-
-struct KParams {
-    uint8_t* D;              // [M, ldd] half
-    const uint32_t* row_bits;   // [M, words]
-    const uint32_t* win_bits;   // [nwin, words]
-    int64_t ldd;
-    int64_t M;
-    int N, K, NG, G;
-    int BN;                  // accumulator width (UMMA N)
-    int n_chunks;            // ceil(N / BN)
-    int words;               // ceil(NG / 32)
-    int kb_per_group;        // G / 64
-    int total_tiles;
-    int ksplit;              // splits of the group range (1 = none); > 1 needs acc32
-    float* acc32;            // [M, N] fp32, zero-filled: partial sums of the splits land here
-    int stages;              // ring depth: kRingBytes / stage_bytes, at most kMaxStages
-    int stage_bytes;         // kAStageBytes + BN * 128
-    int* status;
-};
-
-constexpr size_t kKSmemBytes = 1024 + size_t(kRingBytes) +
-                               (3 * kMaxStages + 4) * sizeof(uint64_t) + 16;
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kKThreads, 1)
@@ -424,6 +393,9 @@ extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw
     if (p.total_tiles < grid) grid = p.total_tiles;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // many token windows and full-width chunks: CTA pairs share each weight tile
+    if (ksplit == 1 && N >= 256 && nwin >= 16 && sm_count() >= 2)
+        return gemm_k_pair_launch(A, lda, W, ldw, p, dtype, s);
     if (ksplit > 1) DPK_CUDA(cudaMemsetAsync(workspace, 0, ws_need, s));
     if (dtype == DPK_BF16) {
         DPK_CUDA(cudaFuncSetAttribute(gemm_k_kernel<true>,

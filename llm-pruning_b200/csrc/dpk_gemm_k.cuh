@@ -1,0 +1,43 @@
+// Definitions shared by the single-CTA and the CTA-pair reduction-width routed GEMM kernels.
+#pragma once
+
+#include "dpk_host.h"
+#include "dpk_sm100.cuh"
+
+namespace dpk {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kAStageBytes = kBM * kBK * 2;
+constexpr int kRingBytes = 4 * (kAStageBytes + 256 * kBK * 2);   // 192 KiB of operand ring
+constexpr int kMaxStages = 12;
+constexpr int kKThreads = 320;
+constexpr int kTmemCols = 512;
+
+struct KParams {
+    uint8_t* D;              // [M, ldd] half
+    const uint32_t* row_bits;   // [M, words]
+    const uint32_t* win_bits;   // [nwin, words]
+    int64_t ldd;
+    int64_t M;
+    int N, K, NG, G;
+    int BN;                  // accumulator width (UMMA N)
+    int n_chunks;            // ceil(N / BN)
+    int words;               // ceil(NG / 32)
+    int kb_per_group;        // G / 64
+    int total_tiles;
+    int ksplit;              // splits of the group range (1 = none); > 1 needs acc32
+    float* acc32;            // [M, N] fp32, zero-filled: partial sums of the splits land here
+    int stages;              // ring depth: kRingBytes / stage_bytes, at most kMaxStages
+    int stage_bytes;         // kAStageBytes + BN * 128
+    int* status;
+};
+
+constexpr size_t kKSmemBytes = 1024 + size_t(kRingBytes) +
+                               (3 * kMaxStages + 4) * sizeof(uint64_t) + 16;
+
+// CTA-pair (cta_group::2) variant, dpk_gemm_k_pair.cu: many token windows, N >= 256.
+int gemm_k_pair_launch(const void* A, int64_t lda, const void* W, int64_t ldw, KParams p, int dtype,
+                       cudaStream_t stream);
+
+}  // namespace dpk

@@ -1,0 +1,314 @@
+// Reduction-width routed projection on CTA pairs (tcgen05 cta_group::2, sm_100a).
+//
+// Same mathematics as dpk_gemm_k.cu for many token windows and N >= 256.  Two CTAs of
+// a cluster own two consecutive 128-token windows and one 256-column output chunk:
+// CTA r loads window (2*pw + r)'s A columns by TMA into its own shared memory, clears
+// the rows of tokens that do not use the group, and loads rows [n0 + 128r, n0 + 128r +
+// 128) of the weight chunk.  One thread of the even CTA issues tcgen05.mma.cta_group::2
+// with M = 256, so every weight byte feeds 256 token rows and each SM reads 16 + 16 KiB
+// per 64-deep K block instead of 16 + 32 KiB.  The pair walks the union of the groups its
+// two windows use; a window's rows are cleared for groups only the other window uses.
+//
+// Barriers.  a_full (each CTA): its own A tile has landed (TMA bytes).  full (even CTA):
+// both weight halves have landed (TMA bytes, the odd CTA's load counts there through the
+// cta_group::2 form) and the 256 fix-up threads of both CTAs have cleared their rows.
+// empty / tfull (both CTAs): multicast commits.  tempty (even CTA): 256 epilogue threads.
+// Every wait is bounded; a cluster barrier precedes the exit.
+#include "dpk_gemm_k.cuh"
+
+namespace dpk {
+
+constexpr int kKPairStageBytes = kAStageBytes + 128 * kBK * 2;    // 32 KiB
+constexpr int kKPairStages = kRingBytes / kKPairStageBytes;       // 6
+constexpr size_t kKPairSmemBytes = 1024 + size_t(kRingBytes) + (3 * kMaxStages + 4) * sizeof(uint64_t) + 16;
+
+struct KPairParams {
+    KParams k;
+    int64_t nwin;       // 128-token windows
+    int pair_tiles;     // ceil(nwin / 2) * n_chunks
+};
+
+template <bool kBf16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kKThreads, 1)
+gemm_k_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
+                   const KPairParams pp)
+{
+    const KParams& p = pp.k;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~uintptr_t(1023));
+    uint64_t* a_full = reinterpret_cast<uint64_t*>(smem + size_t(kRingBytes));
+    uint64_t* full = a_full + kMaxStages;
+    uint64_t* empty = full + kMaxStages;
+    uint64_t* tfull = empty + kMaxStages;
+    uint64_t* tempty = tfull + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int rank = static_cast<int>(cluster_ctarank());
+    const int pair = blockIdx.x >> 1;
+    const int npairs = gridDim.x >> 1;
+
+    if (warp == 4 && lane == 0) {
+        for (int s = 0; s < kKPairStages; ++s) {
+            mbar_init(&a_full[s], 1);       // own A tile: arrive.expect_tx
+            mbar_init(&full[s], 1 + 256);   // even CTA's expect_tx for both weight halves + fix-up threads
+            mbar_init(&empty[s], 1);        // multicast commit
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tfull[b], 1);
+            mbar_init(&tempty[b], 256);
+        }
+        *abort_flag = 0;
+        mbar_init_fence();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmW);
+    }
+    if (warp == 5) tmem_alloc_pair(tmem_slot, kTmemCols);
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // routing bits of window `win`, word `w` (0 beyond the last window)
+    auto win_word = [&](int64_t win, int w) -> uint32_t {
+        return win < pp.nwin ? p.win_bits[win * p.words + w] : 0u;
+    };
+    // groups used by either window of pair-window `pw`
+    auto pair_word = [&](int pw, int w) -> uint32_t {
+        return win_word(2ll * pw, w) | win_word(2ll * pw + 1, w);
+    };
+    auto pair_any = [&](int pw) -> bool {
+        uint32_t any = 0;
+        for (int w = 0; w < p.words; ++w) any |= pair_word(pw, w);
+        return any != 0;
+    };
+    auto decode = [&](int tile, int& pw, int& nchunk) {
+        pw = tile / p.n_chunks;
+        nchunk = tile - pw * p.n_chunks;
+    };
+
+    if (warp < 4) {
+        // ============================ epilogue (own window) ==========================
+        int acc_it = 0;
+        for (int tile = pair; tile < pp.pair_tiles; tile += npairs) {
+            int pw, nchunk;
+            decode(tile, pw, nchunk);
+            const int64_t r = (2ll * pw + rank) * kBM + warp * 32 + lane;
+            const bool valid = r < p.M;
+            const int n0 = nchunk * 256;
+            uint8_t* out = p.D + (r * p.ldd + n0) * 2;
+            if (!pair_any(pw)) {
+                if (valid)
+                    for (int c = 0; c < 256 && n0 + c < p.N; c += 8)
+                        *reinterpret_cast<uint4*>(out + c * 2) = make_uint4(0, 0, 0, 0);
+                continue;
+            }
+            const int ab = acc_it & 1;
+            const bool got = mbar_wait(&tfull[ab], (acc_it >> 1) & 1, abort_flag, p.status,
+                                       DPK_DEV_TIMEOUT_TMEM_FULL);
+            if (!__all_sync(0xffffffffu, got)) break;
+            tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) +
+                                   static_cast<uint32_t>(ab * 256);
+            for (int c = 0; c < 256; c += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(taddr + c, v);
+                tmem_ld_wait();
+                if (valid) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        if (n0 + c + q * 8 < p.N) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                w[j] = pack_half2<kBf16>(__uint_as_float(v[q * 8 + 2 * j]),
+                                                         __uint_as_float(v[q * 8 + 2 * j + 1]));
+                            *reinterpret_cast<uint4*>(out + (c + q * 8) * 2) =
+                                make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive_leader(&tempty[ab]);
+            ++acc_it;
+        }
+    } else if (warp == 4) {
+        // ============================ TMA producer ===================================
+        // own window's A tile -> a_full (local); own half of the weight tile -> the pair's full
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < pp.pair_tiles; tile += npairs) {
+                int pw, nchunk;
+                decode(tile, pw, nchunk);
+                const int a_row = static_cast<int>((2ll * pw + rank) * kBM);
+                const int w_row = nchunk * 256 + rank * 128;
+                for (int w = 0; ok && w < p.words; ++w) {
+                    uint32_t bits = pair_word(pw, w);
+                    while (ok && bits) {
+                        const int g = w * 32 + __ffs(bits) - 1;
+                        bits &= bits - 1;
+                        for (int j = 0; j < p.kb_per_group; ++j) {
+                            if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status,
+                                           DPK_DEV_TIMEOUT_EMPTY)) {
+                                ok = false;
+                                break;
+                            }
+                            uint8_t* sa = smem + size_t(s) * kKPairStageBytes;
+                            const int kcol = g * p.G + j * kBK;
+                            mbar_arrive_expect_tx(&a_full[s], kAStageBytes);
+                            tma_load_2d(sa, &tmA, &a_full[s], kcol, a_row);
+                            if (rank == 0) mbar_arrive_expect_tx(&full[s], 2u * 128 * kBK * 2);
+                            tma_load_2d_pair(sa + kAStageBytes, &tmW, &full[s], kcol, w_row);
+                            if (++s == kKPairStages) { s = 0; ph ^= 1; }
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ============================ UMMA issuer (even CTA only) ====================
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = umma_idesc_f16(kBf16 ? 1 : 0, 256, 256);
+            int s = 0, acc_it = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < pp.pair_tiles; tile += npairs) {
+                int pw, nchunk;
+                decode(tile, pw, nchunk);
+                if (!pair_any(pw)) continue;
+                const int ab = acc_it & 1;
+                if (!mbar_wait(&tempty[ab], ((acc_it >> 1) & 1) ^ 1, abort_flag, p.status,
+                               DPK_DEV_TIMEOUT_TMEM_EMPTY))
+                    break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(ab * 256);
+                uint32_t first = 0;
+                for (int w = 0; ok && w < p.words; ++w) {
+                    uint32_t bits = pair_word(pw, w);
+                    while (ok && bits) {
+                        bits &= bits - 1;
+                        for (int j = 0; j < p.kb_per_group; ++j) {
+                            if (!mbar_wait(&full[s], ph, abort_flag, p.status, DPK_DEV_TIMEOUT_FULL)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            const uint32_t sa = smem_u32(smem + size_t(s) * kKPairStageBytes);
+                            const uint64_t adesc = umma_desc_k_sw128(sa);
+                            const uint64_t bdesc = umma_desc_k_sw128(sa + kAStageBytes);
+#pragma unroll
+                            for (int k = 0; k < kBK / 16; ++k) {
+                                umma_f16_ss_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, first);
+                                first = 1;
+                            }
+                            umma_commit_pair(&empty[s]);
+                            if (++s == kKPairStages) { s = 0; ph ^= 1; }
+                        }
+                    }
+                }
+                if (ok) umma_commit_pair(&tfull[ab]);
+                ++acc_it;
+            }
+        }
+    } else {
+        // ============================ row fix-up (own window) ========================
+        const int wrow0 = (warp - 6) * 32;
+        const int row = wrow0 + lane;
+        const int sub = lane >> 3;
+        const int chunk = lane & 7;
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < pp.pair_tiles; tile += npairs) {
+            int pw, nchunk;
+            decode(tile, pw, nchunk);
+            const int64_t r = (2ll * pw + rank) * kBM + row;
+            const bool in_range = r < p.M;
+            const uint32_t* rb = p.row_bits + (in_range ? r : 0) * p.words;
+            uint32_t next_row = in_range ? rb[0] : 0u;
+            for (int w = 0; ok && w < p.words; ++w) {
+                uint32_t bits = pair_word(pw, w);
+                const uint32_t mine = next_row;
+                if (w + 1 < p.words) next_row = in_range ? rb[w + 1] : 0u;
+                while (ok && bits) {
+                    const int b = __ffs(bits) - 1;
+                    bits &= bits - 1;
+                    const bool active = (mine >> b) & 1u;
+                    const unsigned clear = __ballot_sync(0xffffffffu, !active);
+                    for (int j = 0; j < p.kb_per_group; ++j) {
+                        const bool got = mbar_wait(&a_full[s], ph, abort_flag, p.status,
+                                                   DPK_DEV_TIMEOUT_FULL);
+                        if (!__all_sync(0xffffffffu, got)) {
+                            ok = false;
+                            break;
+                        }
+                        if (clear) {
+                            uint8_t* base = smem + size_t(s) * kKPairStageBytes + (wrow0 + sub) * 128 +
+                                            chunk * 16;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                if ((clear >> (i * 4 + sub)) & 1u)
+                                    *reinterpret_cast<uint4*>(base + i * 4 * 128) =
+                                        make_uint4(0, 0, 0, 0);
+                        }
+                        // also orders the landed A tile before the partner CTA's UMMA issue
+                        fence_proxy_async_smem();
+                        mbar_arrive_leader(&full[s]);
+                        if (++s == kKPairStages) { s = 0; ph ^= 1; }
+                    }
+                }
+            }
+        }
+    }
+
+    if (*abort_flag) __nanosleep(2000000);
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 5) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
+int gemm_k_pair_launch(const void* A, int64_t lda, const void* W, int64_t ldw, KParams p, int dtype,
+                       cudaStream_t s)
+{
+    int grid = sm_count() & ~1;
+    if (grid < 2) return fail(DPK_ERR_UNSUPPORTED, "no CTA pair available");
+    CUtensorMap tmA, tmW;
+    int rc = make_tmap_2d_sw128(&tmA, A, (uint64_t)p.K, (uint64_t)p.M, (uint64_t)lda, kBK, kBM);
+    if (rc) return rc;
+    rc = make_tmap_2d_sw128(&tmW, W, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)ldw, kBK, 128);
+    if (rc) return rc;
+    KPairParams pp;
+    pp.k = p;
+    pp.k.BN = 256;
+    pp.k.n_chunks = (p.N + 255) / 256;
+    pp.k.ksplit = 1;
+    pp.k.acc32 = nullptr;
+    pp.nwin = (p.M + kBM - 1) / kBM;
+    pp.pair_tiles = static_cast<int>((pp.nwin + 1) / 2) * pp.k.n_chunks;
+    if (2 * pp.pair_tiles < grid) grid = 2 * pp.pair_tiles;
+    if (dtype == DPK_BF16) {
+        DPK_CUDA(cudaFuncSetAttribute(gemm_k_pair_kernel<true>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKPairSmemBytes));
+        gemm_k_pair_kernel<true><<<grid, kKThreads, kKPairSmemBytes, s>>>(tmA, tmW, pp);
+    } else {
+        DPK_CUDA(cudaFuncSetAttribute(gemm_k_pair_kernel<false>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKPairSmemBytes));
+        gemm_k_pair_kernel<false><<<grid, kKThreads, kKPairSmemBytes, s>>>(tmA, tmW, pp);
+    }
+    DPK_CUDA(cudaGetLastError());
+    return DPK_OK;
+}
+
+}  // namespace dpk

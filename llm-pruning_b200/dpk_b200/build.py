@@ -29,6 +29,7 @@ SOURCES = [
     "dpk_gemm_mn.cu",
     "dpk_gemm_mn_pair.cu",
     "dpk_gemm_k.cu",
+    "dpk_gemm_k_pair.cu",
     "dpk_gemv.cu",
     "dpk_ffn.cu",
     "dpk_attn_prefill.cu",

@@ -655,3 +655,24 @@ def test_gemm_mn_cta_pairs(ops, M, K, N, NG, fused, dtype):
         assert_rel_active(got, want)
         assert_ref_tol(got, want)
     assert torch.all(got.float().cpu()[0][~mask[0].repeat_interleave(N // NG, dim=-1)] == 0)
+
+
+@pytest.mark.parametrize("M,K,N,NG,dtype", [
+    (2100, 512, 640, 4, torch.bfloat16),     # 17 windows (odd), N tail inside the third chunk
+    (4096, 1024, 256, 16, torch.float16),    # G = 64
+    (2304, 384, 512, 3, torch.bfloat16),
+])
+def test_gemm_k_cta_pairs(ops, M, K, N, NG, dtype):
+    """Many token windows run on CTA pairs: two windows share each weight tile."""
+    g = seeded(M + K)
+    a = torch.randn(1, M, K, generator=g).to(dtype)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(dtype)
+    mask = torch.rand(1, M, NG, generator=g) > 0.5
+    mask[0, 256:512] = False                  # a window pair with no active group
+    mask[0, 640:768] = False                  # one window of a pair inactive
+    mask[0, 1024:1152, 1:] = False            # a window that uses fewer groups than its partner
+    got, _ = ops.gemm_k(dev(a), dev(w), dev(mask))
+    want = O.gemm_k(a.float(), w.float(), mask)
+    assert_rel_active(got, want)
+    assert_ref_tol(got, want)
+    assert torch.all(got.float().cpu()[0, 256:512] == 0)
