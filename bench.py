@@ -431,12 +431,12 @@ def main():
                    "left to the collective",
                    "l2": "inputs larger than L2 (x 64 MiB + weights 336 MiB + h 224 MiB per step)",
                    "seed": SEED},
-        "roofline": {"kernel": "gemm_mn_kernel (fused gate/up + SwiGLU)", "bound": "tensor",
+        "roofline": {"kernel": "gemm_mn_pair_kernel (fused gate/up + SwiGLU, CTA pairs)", "bound": "tensor",
                      "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
                      "peak_source": f"{peak_src} sustained bf16",
                      # dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch
                      # (profiles/gemm_kernels_config2_counters.md); scales with the rank's share
-                     "traffic": (1.188224e9 + 1.156e8) / world if M_TOK == 8192 else None,
+                     "traffic": (1.095717e9 + 1.186e8) / world if M_TOK == 8192 else None,
                      "traffic_source": "ncu capture of one launch at this size, see profiles/",
                      "algorithmic_flops_per_launch": flops_mn},
         "kernels": {"gemm_mn_ms": k_mn, "gemm_k_ms": k_k,
