@@ -28,7 +28,7 @@ namespace dpk {
 
 constexpr int kTcBM = 128;        // query rows per CTA
 constexpr int kTcBN = 64;         // keys per tile
-constexpr int kTcThreads = 320;       // 8 softmax warps + TMA warp + UMMA warp
+constexpr int kTcThreads = 192;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 constexpr int kTcTmemCols = 256;            // 2 x 64 (S) + up to 128 (O)
 
@@ -72,17 +72,6 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
           "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
         : "memory");
 }
-__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&v)[16])
-{
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        :
-        : "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
-          "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]),
-          "r"(v[14]), "r"(v[15])
-        : "memory");
-}
 __device__ __forceinline__ void tmem_st_wait()
 {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -118,10 +107,8 @@ struct TcSmem {
     static constexpr int kOffQ = 0;
     static constexpr int kOffK = kOffQ + kQBytes;
     static constexpr int kOffV = kOffK + 2 * kKBytes;
-    static constexpr int kOffX = kOffV + 2 * kVBytes;          // row maxima exchanged by the two halves
-    static constexpr int kXBytes = 2 * 2 * kTcBM * 4;
-    static constexpr int kOffBar = kOffX + kXBytes;
-    static constexpr int kTotal = kOffBar + 20 * 8 + 16;   // base must be 1024-byte aligned
+    static constexpr int kOffBar = kOffV + 2 * kVBytes;
+    static constexpr int kTotal = kOffBar + 16 * 8 + 16;   // base must be 1024-byte aligned
 };
 
 template <int D, bool kBf16>
@@ -144,9 +131,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     uint64_t* s_full = bars + 9;      // [2]
     uint64_t* p_full = bars + 11;
     uint64_t* pv_done = bars + 12;
-    uint64_t* x_full = bars + 13;     // [2]
-    float* s_x = reinterpret_cast<float*>(smem + L::kOffX);   // [2 buffers][2 halves][128 rows]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -185,8 +170,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const int kv_begin = (lp / kTcBN) * kTcBN;
     const int ntiles = kv_end > kv_begin ? (kv_end - kv_begin + kTcBN - 1) / kTcBN : 0;
 
-    if (warp == 8 && lane == 0) {
-        mbar_init(q_full, 256);
+    if (warp == 4 && lane == 0) {
+        mbar_init(q_full, 128);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&v_full[s], 1);
@@ -194,16 +179,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             mbar_init(&v_empty[s], 1);
             mbar_init(&s_full[s], 1);
         }
-        mbar_init(p_full, 256);
+        mbar_init(p_full, 128);
         mbar_init(pv_done, 1);
-        mbar_init(&x_full[0], 256);
-        mbar_init(&x_full[1], 256);
         *abort_flag = 0;
         mbar_init_fence();
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
     }
-    if (warp == 9) tmem_alloc(tmem_slot, kTcTmemCols);
+    if (warp == 5) tmem_alloc(tmem_slot, kTcTmemCols);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -211,21 +194,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const uint32_t tmem_s0 = tmem_base;            // S buffers: columns [0,64), [64,128)
     const uint32_t tmem_o = tmem_base + 128;       // O: columns [128, 128 + D)
 
-    if (warp < 8) {
-        // =================== softmax / epilogue ==========================================
-        // Two threads per query row: warp q (0-3) and warp q+4 own the same 32 TMEM lanes
-        // (a warp reaches lanes 32*(warp%4)...), the first takes keys [0,32) of every tile,
-        // the second keys [32,64).  They exchange their tile maxima through shared memory
-        // (bounded mbarrier wait), keep identical reference maxima, and each carries the
-        // partial row sum of its own keys.
-        const int half = warp >> 2;
-        const int q4 = warp & 3;
-        const int row = q4 * 32 + lane;
+    if (warp < 4) {
+        // =================== softmax / epilogue: thread = query row =====================
+        const int row = warp * 32 + lane;
         const int tok = token_of(row);
         // gather this CTA's Q rows into the swizzled K-major layout (8 lanes per 128 bytes)
         {
-            const int chunk = threadIdx.x & 7, rsub = threadIdx.x >> 3;   // 32 rows per pass
-            for (int r = rsub; r < kTcBM; r += 32) {
+            const int chunk = threadIdx.x & 7, rsub = threadIdx.x >> 3;   // 16 rows per pass
+            for (int r = rsub; r < kTcBM; r += 16) {
                 const int t = token_of(r);
                 const uint8_t* src_row =
                     t >= 0 ? p.Q + ((static_cast<int64_t>(b) * p.Tq + t) * p.Hq + h) * (D * 2) : p.Q;
@@ -242,11 +218,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             mbar_arrive(q_full);
         }
 
-        constexpr int HC = kTcBN / 2;              // keys per thread and tile
-        constexpr int DH = D / 2;                  // output columns per thread
-        const uint32_t lane_base = static_cast<uint32_t>(q4 * 32) << 16;
+        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
         float m_ref = -INFINITY;    // reference maximum the stored P and O are scaled by
-        float l_sum = 0.f;          // sum over this thread's keys only
+        float l_sum = 0.f;
         bool alive = true;
         for (int j = 0; j < ntiles; ++j) {
             const int sb = j & 1;
@@ -255,40 +229,40 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
             tc_fence_after_sync();
             const uint32_t ts = tmem_s0 + sb * kTcBN + lane_base;
-            const int kv0 = kv_begin + j * kTcBN + half * HC;
-            const bool need_mask = (kv0 < lp) || (kv0 + HC > p.Tk) ||
-                                   (p.causal && kv0 + HC - 1 > first_tok + p.causal_shift);
+            const int kv0 = kv_begin + j * kTcBN;
+            const bool need_mask = (kv0 < lp) || (kv0 + kTcBN > p.Tk) ||
+                                   (p.causal && kv0 + kTcBN - 1 > first_tok + p.causal_shift);
             int lim = p.Tk - 1;
             if (p.causal) lim = min(lim, tok + p.causal_shift);
             if (tok < 0) lim = -1;
 
-            uint32_t sv[HC];
-            tmem_ld_32x32b_x32(ts + half * HC, sv);
-            tmem_ld_wait();
+            // the whole score row of this tile (64 values) stays in registers
+            uint32_t sv[kTcBN];
+            {
+                uint32_t a32[32], b32[32];
+                tmem_ld_32x32b_x32(ts, a32);
+                tmem_ld_32x32b_x32(ts + 32, b32);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) { sv[i] = a32[i]; sv[32 + i] = b32[i]; }
+            }
             if (need_mask) {
 #pragma unroll
-                for (int i = 0; i < HC; ++i) {
+                for (int i = 0; i < kTcBN; ++i) {
                     const int kidx = kv0 + i;
                     if (kidx < lp || kidx > lim) sv[i] = __float_as_uint(-INFINITY);
                 }
             }
+            // row maximum with four independent chains
             float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < HC; i += 4) {
+            for (int i = 0; i < kTcBN; i += 4) {
                 t0 = fmaxf(t0, __uint_as_float(sv[i]));
                 t1 = fmaxf(t1, __uint_as_float(sv[i + 1]));
                 t2 = fmaxf(t2, __uint_as_float(sv[i + 2]));
                 t3 = fmaxf(t3, __uint_as_float(sv[i + 3]));
             }
-            float tmax = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3));
-            // exchange with the thread that owns the other 32 keys of this row
-            float* xb = s_x + sb * (2 * kTcBM);
-            xb[half * kTcBM + row] = tmax;
-            mbar_arrive(&x_full[sb]);
-            const bool gx = mbar_wait(&x_full[sb], (j >> 1) & 1, abort_flag, p.status,
-                                      DPK_DEV_TIMEOUT_FULL);
-            if (!__all_sync(0xffffffffu, gx)) { alive = false; break; }
-            tmax = fmaxf(tmax, xb[(half ^ 1) * kTcBM + row]);
+            const float tmax = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3));
             // lazy reference update: move only when the maximum grew by more than 2^8
             float alpha = 1.f;
             bool moved = false;
@@ -304,10 +278,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             const float ref = m_ref == -INFINITY ? 0.f : m_ref * p.scale_log2;
 
             // P = exp2(scale*S - ref) (masked entries are -inf -> 0), packed to half precision
-            uint32_t pk[HC / 2];
+            uint32_t pk[kTcBN / 2];
             float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < HC; i += 4) {
+            for (int i = 0; i < kTcBN; i += 4) {
                 const float p0 = tc_exp2(fmaf(__uint_as_float(sv[i]), p.scale_log2, -ref));
                 const float p1 = tc_exp2(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -ref));
                 const float p2 = tc_exp2(fmaf(__uint_as_float(sv[i + 2]), p.scale_log2, -ref));
@@ -316,31 +290,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                 pk[i >> 1] = pack_half2<kBf16>(p0, p1);
                 pk[(i >> 1) + 1] = pack_half2<kBf16>(p2, p3);
             }
-            l_sum = l_sum * alpha + ((r0 + r1) + (r2 + r3));
+            const float rs = (r0 + r1) + (r2 + r3);
+            l_sum = l_sum * alpha + rs;
 
             // O may only be rescaled once the previous P V has finished (rare: the reference
-            // maximum of some row of this warp moved); each of the two threads of a row
-            // rescales its half of the columns
+            // maximum of some row of this warp moved)
             if (j > 0 && __any_sync(0xffffffffu, moved)) {
                 const bool ok2 = mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status,
                                            DPK_DEV_TIMEOUT_TMEM_EMPTY);
                 if (!__all_sync(0xffffffffu, ok2)) { alive = false; break; }
                 tc_fence_after_sync();
 #pragma unroll 1
-                for (int c = 0; c < DH; c += 32) {
+                for (int c = 0; c < D; c += 32) {
                     uint32_t v[32];
-                    tmem_ld_32x32b_x32(tmem_o + lane_base + half * DH + c, v);
+                    tmem_ld_32x32b_x32(tmem_o + lane_base + c, v);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
                         v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                    tmem_st_32x32b_x32(tmem_o + lane_base + half * DH + c, v);
+                    tmem_st_32x32b_x32(tmem_o + lane_base + c, v);
                 }
                 tmem_st_wait();
             }
-            // P replaces columns of this tile's S buffer in TMEM (two keys per 32-bit column):
-            // this thread's 32 keys are 16 columns at offset half*16
-            tmem_st_32x32b_x16(ts + half * (HC / 2), pk);
+            // P replaces the first 32 columns of this tile's S buffer in TMEM (two keys per
+            // 32-bit column); the P V UMMA reads its A operand from there
+            tmem_st_32x32b_x32(ts, pk);
             tmem_st_wait();
             tc_fence_before_sync();
             mbar_arrive(p_full);
@@ -353,28 +327,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             alive = __all_sync(0xffffffffu, ok3);
             tc_fence_after_sync();
         }
-        // the row sum is the sum of the two threads' partial sums (same reference maximum)
-        {
-            const int xb_i = ntiles & 1;       // buffer whose last exchange is at least two tiles old
-            float* xb = s_x + xb_i * (2 * kTcBM);
-            if (alive) xb[half * kTcBM + row] = l_sum;
-            mbar_arrive(&x_full[xb_i]);
-            if (alive) {
-                const bool gx = mbar_wait(&x_full[xb_i], (ntiles >> 1) & 1, abort_flag, p.status,
-                                          DPK_DEV_TIMEOUT_FULL);
-                alive = __all_sync(0xffffffffu, gx);
-                if (alive) l_sum += xb[(half ^ 1) * kTcBM + row];
-            }
-        }
         if (alive) {
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
             uint8_t* out = p.O + ((static_cast<int64_t>(b) * p.Tq + (tok >= 0 ? tok : 0)) * p.Hq + h) *
-                                     (D * 2) + half * DH * 2;
+                                     (D * 2);
 #pragma unroll 1
-            for (int c = 0; c < DH; c += 32) {
+            for (int c = 0; c < D; c += 32) {
                 uint32_t v[32];
                 if (ntiles > 0) {
-                    tmem_ld_32x32b_x32(tmem_o + lane_base + half * DH + c, v);
+                    tmem_ld_32x32b_x32(tmem_o + lane_base + c, v);
                     tmem_ld_wait();
                 } else {
 #pragma unroll
@@ -382,18 +343,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                 }
                 if (tok >= 0) {
 #pragma unroll
-                    for (int q8 = 0; q8 < 4; ++q8) {
+                    for (int q4 = 0; q4 < 4; ++q4) {
                         uint32_t w[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
-                            w[i] = pack_half2<kBf16>(__uint_as_float(v[q8 * 8 + 2 * i]) * inv,
-                                                     __uint_as_float(v[q8 * 8 + 2 * i + 1]) * inv);
-                        *reinterpret_cast<uint4*>(out + (c + q8 * 8) * 2) = make_uint4(w[0], w[1], w[2], w[3]);
+                            w[i] = pack_half2<kBf16>(__uint_as_float(v[q4 * 8 + 2 * i]) * inv,
+                                                     __uint_as_float(v[q4 * 8 + 2 * i + 1]) * inv);
+                        *reinterpret_cast<uint4*>(out + (c + q4 * 8) * 2) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
         }
-    } else if (warp == 8) {
+    } else if (warp == 4) {
         // =================== TMA producer: K and V tiles ====================================
         if (lane == 0) {
             const int row_base = b * p.Tk;
@@ -472,7 +433,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     if (*abort_flag) __nanosleep(2000000);
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == 5) {
         __syncwarp();
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTcTmemCols);
