@@ -57,6 +57,11 @@ const char* dpk_last_error(void);
 /*
  * Reads (and clears) the status word kernels write when a bounded wait ran out or a
  * routing index was out of range.  Synchronises `stream`.  *status == 0 means fine.
+ * Otherwise *status = 1000 * kernel + code: code 101/102 a pipeline stage was never
+ * filled / drained, 103/104 the same for an accumulator in tensor memory, 105 a routing
+ * index outside the token range, 106 misaligned shared memory; kernel 1 gemm_mn, 2 gemm_mn
+ * on CTA pairs, 3 gemm_k, 4 gemm_k on CTA pairs, 5 prefill attention, 6 decode attention,
+ * 7 routing.  The first report wins until it is read.
  * The reference's device code has no counterpart: its waits are unbounded
  * (DynamicPruningKernels/include/attention_prefill/v3/sm12x_causal.cuh:401,535).
  */
@@ -250,6 +255,50 @@ size_t dpk_attn_decode_workspace_bytes(int B, int Tk, int Hq, int Hk, int D, int
 int dpk_attn_decode(const void* Q, const void* K, const void* V, const uint8_t* mask,
                     const uint32_t* leftpad, void* O, int B, int Tk, int Hq, int Hk, int D, int NG,
                     float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- tensor parallel: the row-parallel sum fused into the projection ---------------
+ *
+ * The reference runs one process on one GPU and has no collective; it only sketches the
+ * split these calls serve (gate/up/q/k/v column parallel, down/o row parallel,
+ * WIDE/transformer_fsdp_hook.py:44-54, switched off at WIDE/mainloop.py:602).  Rank r
+ * holds the weights of its channel (or head) groups and computes a partial [M,N] sum.
+ * Token rows [o*R, (o+1)*R), R = rows_per_owner (a multiple of 128), are owned by rank o.
+ *
+ *   1. dpk_gemm_k_scatter: dpk_gemm_k whose epilogue stores each token window into slab
+ *      `rank` of the owner's staging buffer stage[o], laid out [world, R, ldd] -- stores
+ *      into peer memory, overlapped with the tiles still being computed.
+ *   2. the caller makes sure every rank has finished step 1 (any barrier between ranks
+ *      that is ordered after the kernel on `stream`, e.g. a one-element all-reduce);
+ *   3. dpk_reduce_gather on every rank: adds the `world` slabs of the rows it owns in
+ *      fp32 (+ an optional residual [M,ld]), rounds once and stores the rows into every
+ *      rank's out[j] ([M,ld]);
+ *   4. a second barrier before anyone reads out[] or starts the next step 1.
+ * No kernel of these waits on another GPU.  world <= 8.
+ */
+
+/* A device buffer other processes of the node can map.  handle: 64 bytes out, to be sent
+ * to the peers by any host channel.  dpk_peer_open maps a peer's buffer into this
+ * process (and enables peer access); close/free undo open/alloc. */
+int dpk_peer_alloc(size_t bytes, void** ptr, void* handle);
+int dpk_peer_open(const void* handle, void** ptr);
+int dpk_peer_close(void* ptr);
+int dpk_peer_free(void* ptr);
+
+size_t dpk_gemm_k_scatter_workspace_bytes(int64_t M, int N, int64_t ldd);
+
+/* Arguments as dpk_gemm_k, with the output replaced by the table of staging buffers
+ * (host array of `world` device pointers, stage[rank] being this rank's own). */
+int dpk_gemm_k_scatter(const void* A, int64_t lda, const void* W, int64_t ldw,
+                       const uint32_t* row_bits, const uint32_t* win_bits, void* const* stage,
+                       int world, int rank, int64_t rows_per_owner, int64_t ldd, int64_t M, int N,
+                       int K, int NG, int dtype, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
+/* stage: this rank's own staging buffer; out: host array of `world` device pointers;
+ * residual: optional local [M,ld] added to the sum (NULL for none). */
+int dpk_reduce_gather(const void* stage, void* const* out, const void* residual, int world,
+                      int rank, int64_t rows_per_owner, int64_t M, int N, int64_t ld, int dtype,
+                      void* stream);
 
 #ifdef __cplusplus
 }

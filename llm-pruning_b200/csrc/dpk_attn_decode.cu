@@ -14,6 +14,7 @@
 //
 // This path is bounded by HBM: algorithmic bytes per launch = 2 * Tk * D * 2 bytes per
 // active (sequence, KV head) pair.
+#define DPK_KERNEL_ID 6   // thousands digit of the device status word
 #include "dpk_host.h"
 #include "dpk_sm100.cuh"
 

@@ -21,6 +21,7 @@
 // keeps the tensor pipe and the exponential unit busy.  All waits are bounded.
 //
 // Algorithmic work per launch: 4*D flops per (active query row, visible key) pair.
+#define DPK_KERNEL_ID 5   // thousands digit of the device status word
 #include "dpk_host.h"
 #include "dpk_sm100.cuh"
 
@@ -147,7 +148,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const int m0 = mt * kTcBM;
     if (m0 >= cnt) return;                          // whole CTA: nothing allocated yet
     if ((smem_u32(smem) & 1023u) != 0u) {           // swizzled tiles need a 1024-byte aligned base
-        if (threadIdx.x == 0) atomicCAS(p.status, 0, DPK_DEV_BAD_SMEM_BASE);
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, 1000 * DPK_KERNEL_ID + DPK_DEV_BAD_SMEM_BASE);
         return;
     }
     const int nrows = min(kTcBM, cnt - m0);
@@ -157,7 +158,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         if (row >= nrows) return -1;
         int64_t t = sidx_b[static_cast<int64_t>(m0 + row) * p.NG + g];
         if (t < 0 || t >= p.Tq) {
-            atomicCAS(p.status, 0, DPK_DEV_BAD_INDEX);
+            atomicCAS(p.status, 0, 1000 * DPK_KERNEL_ID + DPK_DEV_BAD_INDEX);
             return -1;
         }
         return static_cast<int>(t);

@@ -20,6 +20,7 @@
 //
 // Algorithmic work per launch: 2*N*G flops per active (token, group) pair; executed
 // work: 2*N*G*128 per visited (window, group) block.
+#define DPK_KERNEL_ID 3   // thousands digit of the device status word
 #include "dpk_gemm_k.cuh"
 
 namespace dpk {
@@ -325,12 +326,37 @@ extern "C" size_t dpk_gemm_k_workspace_bytes(int64_t M, int N)
     return static_cast<size_t>(M) * N * sizeof(float);
 }
 
-extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw,
-                          const uint32_t* row_bits, const uint32_t* win_bits, void* D, int64_t ldd,
-                          int64_t M, int N, int K, int NG, int dtype, void* workspace,
-                          size_t workspace_bytes, void* stream)
+namespace dpk {
+
+// Where the output goes when it is not the caller's D (tensor-parallel scatter).
+struct PeerOut {
+    void* const* stage;      // [world] staging buffers, one per owner
+    int world, rank;
+    int64_t rows_per_owner;
+};
+
+// rows of a local [M, ldd] matrix -> slab `rank` of the owners' staging buffers
+__global__ void peer_push_rows_kernel(const uint8_t* __restrict__ src, KParams p)
 {
-    DPK_REQUIRE(A && W && D && row_bits && win_bits, "NULL tensor");
+    const int64_t chunks_per_row = p.N / 8;
+    const int64_t total = p.M * chunks_per_row;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = i / chunks_per_row;
+        const int64_t c = i - r * chunks_per_row;
+        const int64_t owner = r / p.rows_per_owner;
+        const int64_t slab_row = int64_t(p.my_rank) * p.rows_per_owner + (r - owner * p.rows_per_owner);
+        *reinterpret_cast<uint4*>(p.peer[owner] + (slab_row * p.ldd + c * 8) * 2) =
+            *reinterpret_cast<const uint4*>(src + (r * p.ldd + c * 8) * 2);
+    }
+}
+
+static int gemm_k_run(const void* A, int64_t lda, const void* W, int64_t ldw,
+                      const uint32_t* row_bits, const uint32_t* win_bits, void* D, int64_t ldd,
+                      int64_t M, int N, int K, int NG, int dtype, void* workspace,
+                      size_t workspace_bytes, void* stream, const PeerOut* peer)
+{
+    DPK_REQUIRE(A && W && (D || peer) && row_bits && win_bits, "NULL tensor");
     DPK_REQUIRE(dtype == DPK_F16 || dtype == DPK_BF16, "dtype must be DPK_F16 or DPK_BF16");
     DPK_REQUIRE(M >= 0 && M < (1ll << 31) && N > 0 && K > 0 && NG > 0, "bad shape");
     DPK_REQUIRE(K % NG == 0, "K=%d is not divisible by NG=%d", K, NG);
@@ -341,6 +367,41 @@ extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw
     DPK_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && ldd % 8 == 0, "row strides must be multiples of 8");
     DPK_REQUIRE(aligned16(A) && aligned16(W) && aligned16(D), "tensors must be 16-byte aligned");
     if (M == 0) return DPK_OK;
+    const int64_t nwin_all = (M + kBM - 1) / kBM;
+    const bool pair_shape = N >= 256 && nwin_all >= 16 && sm_count() >= 2;
+    if (peer) {
+        DPK_REQUIRE(peer->world >= 1 && peer->world <= kMaxPeers, "world must be 1..%d", kMaxPeers);
+        DPK_REQUIRE(peer->rank >= 0 && peer->rank < peer->world, "rank outside the world");
+        DPK_REQUIRE(peer->rows_per_owner > 0 && peer->rows_per_owner % kBM == 0,
+                    "rows_per_owner must be a positive multiple of %d", kBM);
+        DPK_REQUIRE(M <= peer->rows_per_owner * peer->world, "M exceeds world * rows_per_owner");
+        for (int i = 0; i < peer->world; ++i)
+            DPK_REQUIRE(peer->stage[i] && aligned16(peer->stage[i]), "staging buffer %d", i);
+        if (!pair_shape) {
+            // shapes the pair kernel does not take: compute into the workspace, then push rows
+            const size_t split = dpk_gemm_k_workspace_bytes(M, N);
+            const size_t need = split + static_cast<size_t>(M) * ldd * 2;
+            DPK_REQUIRE(workspace && workspace_bytes >= need, "workspace of %zu bytes needed", need);
+            uint8_t* tmp = static_cast<uint8_t*>(workspace) + split;
+            int rc = gemm_k_run(A, lda, W, ldw, row_bits, win_bits, tmp, ldd, M, N, K, NG, dtype,
+                                split ? workspace : nullptr, split, stream, nullptr);
+            if (rc) return rc;
+            KParams q{};
+            q.M = M;
+            q.N = N;
+            q.ldd = ldd;
+            q.world = peer->world;
+            q.my_rank = peer->rank;
+            q.rows_per_owner = peer->rows_per_owner;
+            for (int i = 0; i < peer->world; ++i) q.peer[i] = static_cast<uint8_t*>(peer->stage[i]);
+            const int64_t total = M * (N / 8);
+            int blocks = static_cast<int>((total + 255) / 256);
+            if (blocks > 8 * sm_count()) blocks = 8 * sm_count();
+            peer_push_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(tmp, q);
+            DPK_CUDA(cudaGetLastError());
+            return DPK_OK;
+        }
+    }
 
     int BN = 256;
     if (N < 256) BN = ((N + 15) / 16) * 16;
@@ -388,14 +449,24 @@ extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw
     if (p.stages > kMaxStages) p.stages = kMaxStages;
     p.status = device_status_ptr();
     if (!p.status) return fail(DPK_ERR_CUDA, "no status word on this device");
+    p.world = 0;
+    p.my_rank = 0;
+    p.rows_per_owner = 0;
+    for (int i = 0; i < kMaxPeers; ++i) p.peer[i] = nullptr;
+    if (peer) {
+        p.world = peer->world;
+        p.my_rank = peer->rank;
+        p.rows_per_owner = peer->rows_per_owner;
+        for (int i = 0; i < peer->world; ++i) p.peer[i] = static_cast<uint8_t*>(peer->stage[i]);
+    }
 
     int grid = sm_count();
     if (p.total_tiles < grid) grid = p.total_tiles;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // many token windows and full-width chunks: CTA pairs share each weight tile
-    if (ksplit == 1 && N >= 256 && nwin >= 16 && sm_count() >= 2)
-        return gemm_k_pair_launch(A, lda, W, ldw, p, dtype, s);
+    if (peer) ksplit = 1, p.ksplit = 1, p.acc32 = nullptr, p.total_tiles = (int)(nwin * n_chunks);
+    if (ksplit == 1 && pair_shape) return gemm_k_pair_launch(A, lda, W, ldw, p, dtype, s);
     if (ksplit > 1) DPK_CUDA(cudaMemsetAsync(workspace, 0, ws_need, s));
     if (dtype == DPK_BF16) {
         DPK_CUDA(cudaFuncSetAttribute(gemm_k_kernel<true>,
@@ -417,4 +488,35 @@ extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw
     }
     DPK_CUDA(cudaGetLastError());
     return DPK_OK;
+}
+
+}  // namespace dpk
+
+extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw,
+                          const uint32_t* row_bits, const uint32_t* win_bits, void* D, int64_t ldd,
+                          int64_t M, int N, int K, int NG, int dtype, void* workspace,
+                          size_t workspace_bytes, void* stream)
+{
+    DPK_REQUIRE(D != nullptr, "NULL tensor");
+    return dpk::gemm_k_run(A, lda, W, ldw, row_bits, win_bits, D, ldd, M, N, K, NG, dtype, workspace,
+                           workspace_bytes, stream, nullptr);
+}
+
+extern "C" size_t dpk_gemm_k_scatter_workspace_bytes(int64_t M, int N, int64_t ldd)
+{
+    if (M <= 0 || N <= 0) return 0;
+    const bool pair_shape = N >= 256 && (M + dpk::kBM - 1) / dpk::kBM >= 16;
+    return dpk_gemm_k_workspace_bytes(M, N) + (pair_shape ? 0 : static_cast<size_t>(M) * ldd * 2);
+}
+
+extern "C" int dpk_gemm_k_scatter(const void* A, int64_t lda, const void* W, int64_t ldw,
+                                  const uint32_t* row_bits, const uint32_t* win_bits,
+                                  void* const* stage, int world, int rank, int64_t rows_per_owner,
+                                  int64_t ldd, int64_t M, int N, int K, int NG, int dtype,
+                                  void* workspace, size_t workspace_bytes, void* stream)
+{
+    DPK_REQUIRE(stage != nullptr, "NULL staging table");
+    dpk::PeerOut peer{stage, world, rank, rows_per_owner};
+    return dpk::gemm_k_run(A, lda, W, ldw, row_bits, win_bits, nullptr, ldd, M, N, K, NG, dtype,
+                           workspace, workspace_bytes, stream, &peer);
 }

@@ -13,6 +13,7 @@ constexpr int kRingBytes = 4 * (kAStageBytes + 256 * kBK * 2);   // 192 KiB of o
 constexpr int kMaxStages = 12;
 constexpr int kKThreads = 320;
 constexpr int kTmemCols = 512;
+constexpr int kMaxPeers = 8;
 
 struct KParams {
     uint8_t* D;              // [M, ldd] half
@@ -31,6 +32,12 @@ struct KParams {
     int stages;              // ring depth: kRingBytes / stage_bytes, at most kMaxStages
     int stage_bytes;         // kAStageBytes + BN * 128
     int* status;
+    // Output scattered to the owners of the token windows (tensor parallel; 0 = plain D):
+    // rows [o*rows_per_owner, (o+1)*rows_per_owner) go to slab `my_rank` of peer[o], each slab
+    // [rows_per_owner, ldd].
+    int world, my_rank;
+    int64_t rows_per_owner;
+    uint8_t* peer[kMaxPeers];
 };
 
 constexpr size_t kKSmemBytes = 1024 + size_t(kRingBytes) +

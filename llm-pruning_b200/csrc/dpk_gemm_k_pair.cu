@@ -14,6 +14,14 @@
 // cta_group::2 form) and the 256 fix-up threads of both CTAs have cleared their rows.
 // empty / tfull (both CTAs): multicast commits.  tempty (even CTA): 256 epilogue threads.
 // Every wait is bounded; a cluster barrier precedes the exit.
+//
+// Peer output (kPeer).  Under tensor parallelism the partial sums of a token window go to the
+// rank that owns the window: rows [o*R, (o+1)*R) belong to rank o, and rank r's partial lands in
+// slab r of owner o's staging buffer, a plain pointer into that GPU's memory.  The epilogue
+// transposes each 32 x 64 piece through shared memory so that every store instruction writes
+// four 128-byte row segments -- link packets are filled, which per-thread 16-byte stores to 32
+// different rows would not do.  Nothing here waits on another GPU.
+#define DPK_KERNEL_ID 4   // thousands digit of the device status word
 #include "dpk_gemm_k.cuh"
 
 namespace dpk {
@@ -21,6 +29,10 @@ namespace dpk {
 constexpr int kKPairStageBytes = kAStageBytes + 128 * kBK * 2;    // 32 KiB
 constexpr int kKPairStages = kRingBytes / kKPairStageBytes;       // 6
 constexpr size_t kKPairSmemBytes = 1024 + size_t(kRingBytes) + (3 * kMaxStages + 4) * sizeof(uint64_t) + 16;
+constexpr int kPeerXposeOffset = kRingBytes + 512;        // past the barriers, 128-byte aligned
+constexpr int kPeerXposeBytes = 4 * 32 * 128;             // 4 epilogue warps x 32 rows x 64 halves
+constexpr size_t kKPairPeerSmemBytes = 1024 + size_t(kPeerXposeOffset) + kPeerXposeBytes;
+static_assert((3 * kMaxStages + 4) * sizeof(uint64_t) + 16 <= 512, "barriers overlap the transpose area");
 
 struct KPairParams {
     KParams k;
@@ -28,7 +40,7 @@ struct KPairParams {
     int pair_tiles;     // ceil(nwin / 2) * n_chunks
 };
 
-template <bool kBf16>
+template <bool kBf16, bool kPeer>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kKThreads, 1)
 gemm_k_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                    const KPairParams pp)
@@ -100,11 +112,30 @@ gemm_k_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             const int64_t r = (2ll * pw + rank) * kBM + warp * 32 + lane;
             const bool valid = r < p.M;
             const int n0 = nchunk * 256;
-            uint8_t* out = p.D + (r * p.ldd + n0) * 2;
+            uint8_t* out;                 // local: this thread's row; peer: the warp's first row
+            int64_t rows_left = 0;        // peer: rows of this warp's 32 inside the token range
+            if constexpr (kPeer) {
+                const int64_t row0 = (2ll * pw + rank) * kBM + warp * 32;
+                // (a pair's second window may lie past the last token: it stores nothing)
+                const int64_t owner = min(row0 / p.rows_per_owner, int64_t(p.world - 1));
+                const int64_t slab_row = int64_t(p.my_rank) * p.rows_per_owner +
+                                         (row0 - owner * p.rows_per_owner);
+                out = p.peer[owner] + (slab_row * p.ldd + n0) * 2;
+                rows_left = p.M - row0;
+            } else {
+                out = p.D + (r * p.ldd + n0) * 2;
+            }
             if (!pair_any(pw)) {
-                if (valid)
+                if constexpr (kPeer) {
+                    // the owner sums every slab: an unused window still contributes zeros
+                    if (n0 + lane * 8 < p.N)
+                        for (int i = 0; i < 32 && i < rows_left; ++i)
+                            *reinterpret_cast<uint4*>(out + (int64_t(i) * p.ldd + lane * 8) * 2) =
+                                make_uint4(0, 0, 0, 0);
+                } else if (valid) {
                     for (int c = 0; c < 256 && n0 + c < p.N; c += 8)
                         *reinterpret_cast<uint4*>(out + c * 2) = make_uint4(0, 0, 0, 0);
+                }
                 continue;
             }
             const int ab = acc_it & 1;
@@ -114,6 +145,39 @@ gemm_k_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) +
                                    static_cast<uint32_t>(ab * 256);
+            if constexpr (kPeer) {
+                uint8_t* xp = smem + kPeerXposeOffset + warp * (32 * 128);
+                for (int c = 0; c < 256; c += 64) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t v[32];
+                        tmem_ld_32x32b_x32(taddr + c + 32 * h, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                w[j] = pack_half2<kBf16>(__uint_as_float(v[q * 8 + 2 * j]),
+                                                         __uint_as_float(v[q * 8 + 2 * j + 1]));
+                            // row = lane, 16-byte chunk h*4+q, swizzled by the row: conflict free
+                            *reinterpret_cast<uint4*>(xp + lane * 128 + (((h * 4 + q) ^ (lane & 7)) << 4)) =
+                                make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                    __syncwarp();
+                    const int chunk = lane & 7;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int row = i * 4 + (lane >> 3);
+                        const uint4 val = *reinterpret_cast<const uint4*>(
+                            xp + row * 128 + ((chunk ^ (row & 7)) << 4));
+                        if (row < rows_left && n0 + c + chunk * 8 < p.N)
+                            *reinterpret_cast<uint4*>(out + (int64_t(row) * p.ldd + c + chunk * 8) * 2) = val;
+                    }
+                    __syncwarp();
+                }
+            } else {
             for (int c = 0; c < 256; c += 32) {
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(taddr + c, v);
@@ -132,6 +196,7 @@ gemm_k_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                         }
                     }
                 }
+            }
             }
             tc_fence_before_sync();
             mbar_arrive_leader(&tempty[ab]);
@@ -298,15 +363,22 @@ int gemm_k_pair_launch(const void* A, int64_t lda, const void* W, int64_t ldw, K
     pp.nwin = (p.M + kBM - 1) / kBM;
     pp.pair_tiles = static_cast<int>((pp.nwin + 1) / 2) * pp.k.n_chunks;
     if (2 * pp.pair_tiles < grid) grid = 2 * pp.pair_tiles;
-    if (dtype == DPK_BF16) {
-        DPK_CUDA(cudaFuncSetAttribute(gemm_k_pair_kernel<true>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKPairSmemBytes));
-        gemm_k_pair_kernel<true><<<grid, kKThreads, kKPairSmemBytes, s>>>(tmA, tmW, pp);
+    auto launch = [&](auto kernel, size_t smem_bytes) -> int {
+        DPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem_bytes));
+        kernel<<<grid, kKThreads, smem_bytes, s>>>(tmA, tmW, pp);
+        return DPK_OK;
+    };
+    const bool peer = p.world > 0;
+    if (peer) {
+        if (p.rows_per_owner % kBM) return fail(DPK_ERR_INVALID, "rows_per_owner must be a multiple of 128");
+        rc = dtype == DPK_BF16 ? launch(gemm_k_pair_kernel<true, true>, kKPairPeerSmemBytes)
+                               : launch(gemm_k_pair_kernel<false, true>, kKPairPeerSmemBytes);
     } else {
-        DPK_CUDA(cudaFuncSetAttribute(gemm_k_pair_kernel<false>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kKPairSmemBytes));
-        gemm_k_pair_kernel<false><<<grid, kKThreads, kKPairSmemBytes, s>>>(tmA, tmW, pp);
+        rc = dtype == DPK_BF16 ? launch(gemm_k_pair_kernel<true, false>, kKPairSmemBytes)
+                               : launch(gemm_k_pair_kernel<false, false>, kKPairSmemBytes);
     }
+    if (rc) return rc;
     DPK_CUDA(cudaGetLastError());
     return DPK_OK;
 }

@@ -21,6 +21,7 @@
 // tile i overlaps the main loop of tile i+1.
 //
 // Algorithmic work per launch: 2*K*G flops per active (token, group) pair per weight.
+#define DPK_KERNEL_ID 1   // thousands digit of the device status word
 #include "dpk_gemm_mn.cuh"
 
 namespace dpk {
@@ -137,7 +138,7 @@ gemm_mn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if (valid) {
                 tok = p.sidx[static_cast<int64_t>(slot) * p.NG + g];
                 if (tok < 0 || tok >= p.M) {
-                    atomicCAS(p.status, 0, DPK_DEV_BAD_INDEX);
+                    atomicCAS(p.status, 0, 1000 * DPK_KERNEL_ID + DPK_DEV_BAD_INDEX);
                     valid = false;
                 }
             }

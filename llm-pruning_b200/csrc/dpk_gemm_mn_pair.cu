@@ -18,6 +18,7 @@
 // The accumulator-drained barrier is in the even CTA; the odd CTA's epilogue threads
 // arrive on it remotely.  Every wait is bounded; a cluster barrier precedes the exit so
 // that no CTA leaves while its partner can still touch its shared memory.
+#define DPK_KERNEL_ID 2   // thousands digit of the device status word
 #include "dpk_gemm_mn.cuh"
 
 namespace dpk {
@@ -131,7 +132,7 @@ gemm_mn_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             if (valid) {
                 tok = p.sidx[static_cast<int64_t>(slot) * p.NG + g];
                 if (tok < 0 || tok >= p.M) {
-                    atomicCAS(p.status, 0, DPK_DEV_BAD_INDEX);
+                    atomicCAS(p.status, 0, 1000 * DPK_KERNEL_ID + DPK_DEV_BAD_INDEX);
                     valid = false;
                 }
             }

@@ -1,0 +1,156 @@
+// Tensor-parallel plumbing that lives next to the kernels: buffers another process of the
+// node can map (CUDA IPC), and the second half of the fused row-parallel sum.
+//
+// The first half is the epilogue of the reduction-width projection (dpk_gemm_k_scatter):
+// every rank stores its partial sums of a token window straight into the staging buffer
+// of the rank that owns the window.  After all ranks have finished that kernel (the
+// caller's barrier), dpk_reduce_gather on owner o adds the `world` slabs of its rows in
+// fp32, optionally adds a residual, rounds once and stores the rows into every rank's
+// output -- again plain stores into peer memory, 16 bytes per thread and 512 contiguous
+// bytes per warp.  No kernel here waits for another GPU.
+#define DPK_KERNEL_ID 8   // thousands digit of the device status word
+#include "dpk_host.h"
+#include "dpk_sm100.cuh"
+
+namespace dpk {
+
+constexpr int kMaxPeersRG = 8;
+
+struct ReduceGatherParams {
+    const uint8_t* stage;            // [world, rows_per_owner, ld] halves (this rank's staging)
+    const uint8_t* residual;         // [M, ld] halves or NULL (local)
+    uint8_t* out[kMaxPeersRG];       // every rank's [M, ld] output
+    int world, rank;
+    int64_t rows_per_owner, rows;    // rows = owned rows inside the token range
+    int64_t ld;
+    int N;
+};
+
+template <bool kBf16>
+__device__ __forceinline__ void accumulate8(float (&acc)[8], const uint4& v)
+{
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float lo, hi;
+        unpack_half2<kBf16>(w[j], lo, hi);
+        acc[2 * j] += lo;
+        acc[2 * j + 1] += hi;
+    }
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(256) reduce_gather_kernel(const ReduceGatherParams p)
+{
+    const int64_t chunks_per_row = p.N / 8;
+    const int64_t total = p.rows * chunks_per_row;
+    const int64_t slab = p.rows_per_owner * p.ld * 2;                 // bytes
+    const int64_t first_row = int64_t(p.rank) * p.rows_per_owner;     // in the full matrix
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = i / chunks_per_row;
+        const int64_t c = i - r * chunks_per_row;
+        const int64_t off = (r * p.ld + c * 8) * 2;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        // the slabs are summed in rank order on every owner: the result does not depend on
+        // which rank computes it
+        for (int j = 0; j < p.world; ++j)
+            accumulate8<kBf16>(acc, *reinterpret_cast<const uint4*>(p.stage + j * slab + off));
+        const int64_t goff = ((first_row + r) * p.ld + c * 8) * 2;
+        if (p.residual) accumulate8<kBf16>(acc, *reinterpret_cast<const uint4*>(p.residual + goff));
+        uint4 o;
+        o.x = pack_half2<kBf16>(acc[0], acc[1]);
+        o.y = pack_half2<kBf16>(acc[2], acc[3]);
+        o.z = pack_half2<kBf16>(acc[4], acc[5]);
+        o.w = pack_half2<kBf16>(acc[6], acc[7]);
+        for (int j = 0; j < p.world; ++j) {
+            // start with the neighbour so that the ranks do not all store to the same peer at once
+            const int dst = (p.rank + 1 + j) % p.world;
+            *reinterpret_cast<uint4*>(p.out[dst] + goff) = o;
+        }
+    }
+}
+
+}  // namespace dpk
+
+using namespace dpk;
+
+extern "C" int dpk_peer_alloc(size_t bytes, void** ptr, void* handle)
+{
+    DPK_REQUIRE(ptr && handle && bytes > 0, "bad arguments");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    void* p = nullptr;
+    DPK_CUDA(cudaMalloc(&p, bytes));
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return fail(DPK_ERR_CUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+    }
+    memcpy(handle, &h, sizeof(h));
+    *ptr = p;
+    return DPK_OK;
+}
+
+extern "C" int dpk_peer_open(const void* handle, void** ptr)
+{
+    DPK_REQUIRE(ptr && handle, "bad arguments");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    DPK_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return DPK_OK;
+}
+
+extern "C" int dpk_peer_close(void* ptr)
+{
+    DPK_REQUIRE(ptr, "NULL pointer");
+    DPK_CUDA(cudaIpcCloseMemHandle(ptr));
+    return DPK_OK;
+}
+
+extern "C" int dpk_peer_free(void* ptr)
+{
+    DPK_REQUIRE(ptr, "NULL pointer");
+    DPK_CUDA(cudaFree(ptr));
+    return DPK_OK;
+}
+
+extern "C" int dpk_reduce_gather(const void* stage, void* const* out, const void* residual, int world,
+                                 int rank, int64_t rows_per_owner, int64_t M, int N, int64_t ld,
+                                 int dtype, void* stream)
+{
+    DPK_REQUIRE(stage && out, "NULL tensor");
+    DPK_REQUIRE(dtype == DPK_F16 || dtype == DPK_BF16, "dtype must be DPK_F16 or DPK_BF16");
+    DPK_REQUIRE(world >= 1 && world <= kMaxPeersRG, "world must be 1..%d", kMaxPeersRG);
+    DPK_REQUIRE(rank >= 0 && rank < world, "rank outside the world");
+    DPK_REQUIRE(rows_per_owner > 0 && M >= 0 && M <= rows_per_owner * world, "bad row split");
+    DPK_REQUIRE(N > 0 && N % 8 == 0 && ld >= N && ld % 8 == 0, "N and ld must be multiples of 8");
+    DPK_REQUIRE(aligned16(stage) && aligned16(residual), "tensors must be 16-byte aligned");
+    ReduceGatherParams p;
+    p.stage = static_cast<const uint8_t*>(stage);
+    p.residual = static_cast<const uint8_t*>(residual);
+    for (int i = 0; i < kMaxPeersRG; ++i) p.out[i] = nullptr;
+    for (int i = 0; i < world; ++i) {
+        DPK_REQUIRE(out[i] && aligned16(out[i]), "output %d", i);
+        p.out[i] = static_cast<uint8_t*>(out[i]);
+    }
+    p.world = world;
+    p.rank = rank;
+    p.rows_per_owner = rows_per_owner;
+    const int64_t first = int64_t(rank) * rows_per_owner;
+    p.rows = M - first < 0 ? 0 : (M - first > rows_per_owner ? rows_per_owner : M - first);
+    p.ld = ld;
+    p.N = N;
+    if (p.rows == 0) return DPK_OK;
+    const int64_t total = p.rows * (N / 8);
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = int64_t(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == DPK_BF16)
+        reduce_gather_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, s>>>(p);
+    else
+        reduce_gather_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, s>>>(p);
+    DPK_CUDA(cudaGetLastError());
+    return DPK_OK;
+}

@@ -6,6 +6,7 @@
 // bytes).  Reads go through a shared-memory tile so that global accesses are
 // row-contiguous; writes of sorted_indices are 8-byte scatters by construction of
 // the [M,NG] layout the operator API returns.
+#define DPK_KERNEL_ID 7   // thousands digit of the device status word
 #include "dpk_host.h"
 #include "dpk_sm100.cuh"
 

@@ -26,6 +26,10 @@ enum : int {
 };
 
 // about one second at 2 GHz
+// Each translation unit may name itself; the status word then reads 1000 * id + code.
+#ifndef DPK_KERNEL_ID
+#define DPK_KERNEL_ID 0
+#endif
 #ifndef DPK_WAIT_LIMIT_CYCLES
 #define DPK_WAIT_LIMIT_CYCLES (2000000000ll)
 #endif
@@ -113,7 +117,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             if (*abort_flag) return false;
             if (clock64() - t0 > DPK_WAIT_LIMIT_CYCLES) {
                 *abort_flag = 1;
-                if (status) atomicCAS(status, 0, code);
+                if (status) atomicCAS(status, 0, 1000 * DPK_KERNEL_ID + code);
                 return false;
             }
         }
@@ -350,6 +354,21 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
     } else {
         __half2 v = __floats2half2_rn(lo, hi);
         return *reinterpret_cast<uint32_t*>(&v);
+    }
+}
+
+
+template <bool kBf16>
+__device__ __forceinline__ void unpack_half2(uint32_t w, float& lo, float& hi)
+{
+    if constexpr (kBf16) {
+        // bf16 is the upper half of an fp32
+        lo = __uint_as_float(w << 16);
+        hi = __uint_as_float(w & 0xffff0000u);
+    } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+        lo = f.x;
+        hi = f.y;
     }
 }
 

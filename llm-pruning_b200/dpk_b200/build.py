@@ -35,6 +35,7 @@ SOURCES = [
     "dpk_attn_prefill.cu",
     "dpk_attn_prefill_tc.cu",
     "dpk_attn_decode.cu",
+    "dpk_peer.cu",
 ]
 
 NVCC_FLAGS = [

@@ -54,11 +54,15 @@ class RoutedFFN:
         self.acc_bytes = self.lib.dpk_gemm_k_workspace_bytes(M, H)
         self.acc = torch.empty(max(self.acc_bytes, 16), dtype=u8, device=dev)
         self.launches_per_call = 3 + 1 + 1       # routing plan (3 kernels), gate/up, down
+        # tensor-parallel ranks: a dpk_b200.peer.RowParallelSum of width H makes the down
+        # projection store its partial sums into the owners' memory and return the summed y
+        self.row_parallel = None
 
     def __call__(self, x: torch.Tensor, mask: torch.Tensor, out: Optional[torch.Tensor] = None,
                  events: Optional[Dict[str, List[Tuple[torch.cuda.Event, torch.cuda.Event]]]] = None,
                  row_chunks: int = 1,
-                 chunk_done: Optional[Callable[[torch.Tensor], None]] = None) -> torch.Tensor:
+                 chunk_done: Optional[Callable[[torch.Tensor], None]] = None,
+                 residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``x``: ``[..., H]``; ``mask``: ``[..., NG]`` (bool / 0-1).  When ``events``
         is a dict, CUDA event pairs bracketing the two GEMM kernels are appended to
         ``events["gemm_mn"]`` and ``events["gemm_k"]``.
@@ -66,7 +70,11 @@ class RoutedFFN:
         ``row_chunks > 1`` runs the down projection in that many token chunks (multiples
         of 128 rows) and calls ``chunk_done(y_rows)`` after each launch -- the hook a
         tensor-parallel caller uses to start the all-reduce of a finished chunk while the
-        next one is being computed."""
+        next one is being computed.
+
+        With ``self.row_parallel`` set the down projection is the fused row-parallel sum
+        instead: the result (plus ``residual [..., H]`` when given) is the sum over the
+        ranks, returned as a view of the shared output buffer."""
         lead = x.shape[:-1]
         xf = x.reshape(-1, self.H)
         if not xf.is_contiguous():
@@ -93,6 +101,17 @@ class RoutedFFN:
         if ev is not None:
             ev[1].record()
             ev[2].record()
+        if self.row_parallel is not None:
+            res2 = residual.reshape(M, H) if residual is not None else None
+            ysum = self.row_parallel.gemm_k(self.h[:M], self.wd, self.row_bits, self.win_bits, NG,
+                                            residual=res2)
+            if ev is not None:
+                ev[3].record()
+                events.setdefault("gemm_mn", []).append((ev[0], ev[1]))
+                events.setdefault("gemm_k", []).append((ev[2], ev[3]))
+            return ysum.view(*lead, H)
+        if residual is not None:
+            raise ValueError("residual is only fused into the row-parallel sum")
         words = self.row_bits.shape[1]
         step = M if row_chunks <= 1 else max(128, ((M + row_chunks - 1) // row_chunks + 127) // 128 * 128)
         esz = y.element_size()

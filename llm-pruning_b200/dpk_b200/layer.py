@@ -12,6 +12,15 @@ the two reductions cannot be merged.
 This mirrors the data flow of ``WrapperDecoderLayer.forward``
 (``WIDE/wrapper/attn_group_ffn_block.py:148-218``) with the routing masks given;
 normalisation, rotary embedding and the routers themselves are outside this class.
+
+With ``token_chunks > 1`` (tensor-parallel ranks, one sequence) the layer runs as a
+software pipeline over chunks of query rows: projections for all tokens, then per chunk
+attention + output projection, whose all-reduce runs on the collective's stream while
+the next chunk's attention is computed; the FFN of a chunk starts as soon as that
+chunk's first reduction has landed, and its second reduction overlaps the next chunk's
+FFN.  Only the last chunk's second reduction is exposed.  A chunk of query rows
+``[s,e)`` attends to keys ``[0,e)`` with the causal diagonal aligned to the bottom
+right, which is exactly the causal mask of those rows in the full sequence.
 """
 
 from __future__ import annotations
@@ -40,6 +49,19 @@ class RoutedDecoderLayer:
         self.pg = process_group
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
         self.timers = None          # optional dict of CUDA event pairs per phase
+        self.token_chunks = 1       # > 1: pipelined forward (see the module docstring)
+        self.sum_o = None           # dpk_b200.peer.RowParallelSum pair: see fuse_sums()
+        self.H = wo.shape[0]
+
+    def fuse_sums(self, max_tokens: int) -> None:
+        """Replace the two all-reduces by the fused row-parallel sums of
+        :mod:`dpk_b200.peer`: the output and down projections store their partial sums
+        into the owning ranks' memory, and the residual additions ride on the reduction.
+        Collective over the process group (buffers are exchanged)."""
+        from .peer import RowParallelSum
+        dev, dt = self.wo.device, self.wo.dtype
+        self.sum_o = RowParallelSum.connect(max_tokens, self.H, dt, dev, self.pg)
+        self.ffn.row_parallel = RowParallelSum.connect(max_tokens, self.H, dt, dev, self.pg)
 
     def _mark(self, name):
         if self.timers is not None:
@@ -51,6 +73,8 @@ class RoutedDecoderLayer:
         """``x [B,T,H]`` (replicated), ``attn_mask [B,T,attn_groups]`` and ``ffn_mask
         [B,T,ffn_groups]`` (this rank's columns).  Returns the layer output ``[B,T,H]``."""
         B, T, H = x.shape
+        if self.token_chunks > 1 and B == 1 and T >= 256 * self.token_chunks:
+            return self._pipelined(x, attn_mask, ffn_mask)
         self._mark("start")
         q, meta = ops.gemm_mn(x, self.wq, attn_mask)
         k = (x @ self.wk.T).view(B, T, self.Hk, self.D)
@@ -59,6 +83,16 @@ class RoutedDecoderLayer:
         meta_attn = meta if B == 1 else {}       # per-batch vs flattened layouts differ for B > 1
         attn, _ = ops.attention_prefill(q.view(B, T, self.Hq, self.D), k, v, attn_mask, **meta_attn)
         self._mark("attn")
+        if self.sum_o is not None:
+            # x1 = x + sum over ranks of o; layer output = x1 + sum over ranks of y
+            x1 = self.sum_o.routed_gemm_k(attn.view(B, T, self.Hq * self.D), self.wo, attn_mask,
+                                          residual=x.contiguous())
+            self._mark("oproj")
+            self._mark("ar1")
+            out = self.ffn(x1, ffn_mask, residual=x1)
+            self._mark("ffn")
+            self._mark("ar2")
+            return out
         o, _ = ops.gemm_k(attn.view(B, T, self.Hq * self.D), self.wo, attn_mask, **meta)
         self._mark("oproj")
         if self.world > 1:
@@ -71,3 +105,33 @@ class RoutedDecoderLayer:
             dist.all_reduce(y, group=self.pg)
         self._mark("ar2")
         return x1 + y
+
+    def _pipelined(self, x: torch.Tensor, attn_mask: torch.Tensor, ffn_mask: torch.Tensor) -> torch.Tensor:
+        _, T, H = x.shape
+        step = ((T + self.token_chunks - 1) // self.token_chunks + 127) // 128 * 128
+        spans = [(s, min(s + step, T)) for s in range(0, T, step)]
+        q, meta = ops.gemm_mn(x, self.wq, attn_mask)
+        k = (x @ self.wk.T).view(1, T, self.Hk, self.D)
+        v = (x @ self.wv.T).view(1, T, self.Hk, self.D)
+        q = q.view(1, T, self.Hq, self.D)
+        nopad = torch.zeros(1, dtype=torch.int32, device=x.device)     # selects bottom-right alignment
+        o = torch.empty_like(x)
+        y = torch.empty_like(x)
+        x1 = torch.empty_like(x)
+        ar1, ar2 = [], []
+        for s, e in spans:
+            am = attn_mask[:, s:e]
+            attn, meta_c = ops.attention_prefill(q[:, s:e], k[:, :e], v[:, :e], am, Leftpad=nopad)
+            ops.gemm_k(attn.view(1, e - s, self.Hq * self.D), self.wo, am, D=o[:, s:e], **meta_c)
+            ar1.append(dist.all_reduce(o[:, s:e], group=self.pg, async_op=True)
+                       if self.world > 1 else None)
+        for (s, e), work in zip(spans, ar1):
+            if work is not None:
+                work.wait()                               # the compute stream waits, not the host
+            torch.add(x[:, s:e], o[:, s:e], out=x1[:, s:e])
+            self.ffn(x1[:, s:e], ffn_mask[:, s:e], out=y[:, s:e])
+            if self.world > 1:
+                ar2.append(dist.all_reduce(y[:, s:e], group=self.pg, async_op=True))
+        for work in ar2:
+            work.wait()
+        return x1.add_(y)

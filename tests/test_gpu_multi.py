@@ -1,0 +1,82 @@
+"""Fused row-parallel sum on real peers (needs at least two GPUs; skipped otherwise).
+Each rank is one process; the partial sums travel through mapped peer memory.  The result
+is compared with the same partial sums added by an NCCL all-reduce and with the oracle."""
+
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    sys.path[:0] = [ROOT, os.path.join(ROOT, "llm-pruning_b200")]
+    import torch.distributed as dist
+    from dpk_b200 import ops, tp
+    from dpk_b200.ffn import RoutedFFN
+    from dpk_b200.peer import RowParallelSum
+    from oracle import dpk_oracle as O
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        bf = torch.bfloat16
+        g = torch.Generator().manual_seed(5)                  # replicated inputs
+        M, H, I, NG = 2100, 512, 2048, 16
+        x = torch.randn(1, M, H, generator=g).to(bf)
+        wg = (torch.randn(I, H, generator=g) * 0.05).to(bf)
+        wu = (torch.randn(I, H, generator=g) * 0.05).to(bf)
+        wd = (torch.randn(H, I, generator=g) * 0.05).to(bf)
+        mask = O.topk_route_mask(torch.randn(1, M, NG, generator=g), NG // 2)
+        lg, lu, ld = (t.to(dev) for t in tp.shard_ffn_weights(wg, wu, wd, NG, world, rank))
+        lmask = tp.shard_mask(mask, world, rank).to(dev)
+        ffn = RoutedFFN(lg, lu, ld, NG // world, M)
+        xd = x.to(dev)
+        y_nccl = ffn(xd, lmask).clone()
+        dist.all_reduce(y_nccl)
+        y_nccl = y_nccl + xd
+        ffn.row_parallel = RowParallelSum.connect(M, H, bf, dev)
+        for _ in range(3):                                    # buffers are reused call after call
+            y = ffn(xd, lmask, residual=xd)
+        torch.cuda.synchronize()
+        want = x.float() + O.ffn_swiglu(x.float(), wg.float(), wu.float(), wd.float(), mask,
+                                        round_intermediate=bf)
+        ret[rank] = dict(
+            vs_nccl=O.rel_err(y.float().cpu(), y_nccl.float().cpu()),
+            vs_oracle=O.rel_err(y.float().cpu(), want),
+            status=ops.device_status(),
+            digest=float(y.float().sum().item()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_row_parallel_ffn_two_ranks():
+    world = 2
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+        out = dict(ret)
+    assert sorted(out) == list(range(world))
+    for r in range(world):
+        assert out[r]["status"] == 0
+        assert out[r]["vs_oracle"] <= 2e-2, out[r]
+        # one rounding of the sum instead of one per partial and one for the residual
+        assert out[r]["vs_nccl"] <= 2e-2, out[r]
+    assert out[0]["digest"] == out[1]["digest"]       # both ranks hold the same bits

@@ -529,6 +529,38 @@ def test_routed_decoder_layer_single_rank(ops):
     assert_rel(out, want, tol=3e-2)
 
 
+def test_routed_decoder_layer_token_chunk_pipeline(ops):
+    """The pipelined schedule (query-row chunks, each attending to the keys up to its own
+    end with the causal diagonal at the bottom right) computes what the one-pass schedule
+    computes: same kernels on row subsets, so the two agree to within a bf16 rounding of
+    the attention accumulation order, and both match the oracle composition."""
+    from dpk_b200.layer import RoutedDecoderLayer
+
+    bf = torch.bfloat16
+    g = seeded(22)
+    T, H, Hq, Hk, D, I, NGF = 1100, 256, 8, 2, 64, 1024, 8
+    ws = {n: bf16r(torch.randn(*shp, generator=g) * 0.05) for n, shp in dict(
+        wq=(Hq * D, H), wk=(Hk * D, H), wv=(Hk * D, H), wo=(H, Hq * D),
+        wg=(I, H), wu=(I, H), wd=(H, I)).items()}
+    x = bf16r(torch.randn(1, T, H, generator=g))
+    am = torch.rand(1, T, Hk, generator=g) > 0.3
+    fm = O.topk_route_mask(torch.randn(1, T, NGF, generator=g), 4)
+    layer = RoutedDecoderLayer(*(dev(ws[n], bf) for n in ("wq", "wk", "wv", "wo", "wg", "wu", "wd")),
+                               num_q_heads=Hq, num_kv_heads=Hk, head_dim=D, attn_groups=Hk,
+                               ffn_groups=NGF, max_tokens=T)
+    one_pass = layer(dev(x, bf), dev(am), dev(fm))
+    layer.token_chunks = 3                       # 384-row chunks, the last one ragged (332 rows)
+    chunked = layer(dev(x, bf), dev(am), dev(fm))
+    assert_rel(chunked, one_pass.float().cpu(), tol=1e-2)
+    q = bf16r(O.gemm_mn(x, ws["wq"], am)).view(1, T, Hq, D)
+    k = bf16r(x @ ws["wk"].T).view(1, T, Hk, D)
+    v = bf16r(x @ ws["wv"].T).view(1, T, Hk, D)
+    a = bf16r(O.attention_prefill(q, k, v, am)).view(1, T, Hq * D)
+    x1 = bf16r(x + bf16r(O.gemm_k(a, ws["wo"], am)))
+    want = x1 + O.ffn_swiglu(x1, ws["wg"], ws["wu"], ws["wd"], fm, round_intermediate=bf)
+    assert_rel(chunked, want, tol=3e-2)
+
+
 def test_prefill_cross_length(ops):
     """Tq != Tk: top-left causal alignment without Leftpad, bottom-right with it -- the two
     behaviours of the reference's PyTorch path (references.py:123-139)."""
@@ -676,3 +708,46 @@ def test_gemm_k_cta_pairs(ops, M, K, N, NG, dtype):
     assert_rel_active(got, want)
     assert_ref_tol(got, want)
     assert torch.all(got.float().cpu()[0, 256:512] == 0)
+
+
+@pytest.mark.parametrize("world,M,N,Kl,NGl", [(4, 2100, 512, 256, 4),     # CTA-pair kernel, ragged end
+                                              (2, 4096, 256, 512, 4),     # CTA-pair kernel, even split
+                                              (8, 2304, 320, 128, 2),     # N not a multiple of 256
+                                              (2, 300, 256, 256, 4),      # few windows: push kernel
+                                              (3, 40, 64, 128, 2)])       # narrow output, one window
+def test_row_parallel_sum_emulated_ranks(ops, world, M, N, Kl, NGl):
+    """The fused row-parallel sum with all ranks emulated on one GPU: every rank's
+    projection stores its partial windows into the owners' staging slabs, every owner
+    reduces and hands the rows to all ranks.  Every rank's output must be the sum of the
+    per-rank oracle projections (plus the residual)."""
+    from dpk_b200.peer import RowParallelSum
+
+    bf = torch.bfloat16
+    g = seeded(1000 * world + M)
+    ranks = RowParallelSum.emulate(world, M, N, bf, torch.device("cuda"))
+    a = [bf16r(torch.randn(1, M, Kl, generator=g)) for _ in range(world)]
+    w = [bf16r(torch.randn(N, Kl, generator=g) / (Kl * world) ** 0.5) for _ in range(world)]
+    mask = [torch.rand(1, M, NGl, generator=g) > 0.5 for _ in range(world)]
+    if M >= 256:
+        mask[0][0, 128:256] = False          # a window rank 0 contributes only zeros to
+    res = bf16r(torch.randn(M, N, generator=g))
+    want = sum(O.gemm_k(a[r], w[r], mask[r]) for r in range(world))[0]
+    words = (NGl + 31) // 32
+    lib = ranks[0].lib
+    for use_res in (False, True):
+        for r in range(world):               # first halves of all ranks ...
+            m8 = dev(mask[r][0]).to(torch.uint8).contiguous()
+            rb = torch.empty((M, words), dtype=torch.int32, device="cuda")
+            wb = torch.empty(((M + 127) // 128, words), dtype=torch.int32, device="cuda")
+            assert lib.dpk_mask_pack(m8.data_ptr(), M, NGl, rb.data_ptr(), wb.data_ptr(), None) == 0
+            ranks[r].scatter(dev(a[r][0], bf), dev(w[r], bf), rb, wb, NGl)
+        outs = []
+        for r in range(world):               # ... then the second halves
+            outs.append(ranks[r].reduce(M, dev(res, bf) if use_res else None))
+        expect = want + res if use_res else want
+        # every partial sum crosses the link as bf16 and the total is rounded once more:
+        # world + 1 roundings where the single-rank projection has one (held to 2e-2 above)
+        for r in range(world):
+            assert_rel(outs[r], expect, tol=3e-2)
+        for r in range(1, world):            # and the ranks agree bit for bit
+            assert torch.equal(outs[r], outs[0])
