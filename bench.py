@@ -217,6 +217,10 @@ def main():
                          "profiler captures only and are named in config.workload)")
     ap.add_argument("--skip-e2e", action="store_true", help="profiler captures only")
     ap.add_argument("--skip-dense", action="store_true", help="profiler captures only")
+    ap.add_argument("--sum", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: how the ranks' partial outputs are added: 'fused' = the down "
+                         "projection stores its partial windows into the owning rank's memory and a "
+                         "reduce+gather kernel finishes the sum; 'nccl' = NCCL all-reduce")
     ap.add_argument("--ar-chunks", type=int, default=0,
                     help="N > 1: token chunks of the down projection whose all-reduces overlap "
                          "the next chunk's compute (0 = automatic: 4 chunks on 2 GPUs, where the "
@@ -265,6 +269,11 @@ def main():
     logits = logits_host.to(device)
     y = torch.empty(M_TOK, HID, dtype=torch.bfloat16, device=device)
 
+    fused = world > 1 and args.sum == "fused"
+    if fused:
+        from dpk_b200.peer import RowParallelSum
+        ffn.row_parallel = RowParallelSum.connect(M_TOK, HID, torch.bfloat16, device)
+        args.ar_chunks, args.sm_margin = 1, 0
     if args.ar_chunks <= 0:
         args.ar_chunks = 4 if world == 2 else 1
     chunks = args.ar_chunks if world > 1 else 1
@@ -279,6 +288,8 @@ def main():
         if world == 1:
             ffn(x_in, mask, out=y_out, events=events)
             return y_out
+        if fused:
+            return ffn(x_in, mask[:, groups[0]:groups[1]], events=events)    # shared output buffer
         works = []
         ffn(x_in, mask[:, groups[0]:groups[1]], out=y_out, events=events, row_chunks=chunks,
             chunk_done=lambda rows: works.append(dist.all_reduce(rows, async_op=True)))
@@ -286,7 +297,7 @@ def main():
             wk.wait()
         return y_out
 
-    launches_per_step = 1 + ffn.launches_per_call + (chunks - 1)
+    launches_per_step = 1 + ffn.launches_per_call + (1 if fused else chunks - 1)
 
     # ---- device-resident timing -----------------------------------------------------
     for _ in range(args.warmup):
@@ -356,7 +367,9 @@ def main():
                 dist.broadcast(ld[b], src=0)
             if ev_out[b] is not None:
                 s_cmp.wait_event(ev_out[b])              # y buffer b has been read back
-            step(None, xd[b], ld[b], yd[b])
+            res = step(None, xd[b], ld[b], yd[b])
+            if fused and rank == 0:
+                yd[b].copy_(res)     # the shared output buffer is overwritten by the next step
             ev_cmp[b] = torch.cuda.Event()
             ev_cmp[b].record(s_cmp)
             if rank == 0:                                # the reduced result is identical on every rank
@@ -426,9 +439,13 @@ def main():
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD,
                    "parallelism": "single GPU" if world == 1 else
-                   f"tp{world} by channel groups ({gpr} groups per rank) + NCCL all-reduce of y in "
-                   f"{chunks} token chunks overlapping the down projection, {args.sm_margin} SMs "
-                   "left to the collective",
+                   (f"tp{world} by channel groups ({gpr} groups per rank); the down projection stores "
+                    "its partial token windows into the owning rank's memory (NVLink), a reduce+gather "
+                    "kernel adds them and hands the rows to every rank; two one-element all-reduces as "
+                    "barriers" if fused else
+                    f"tp{world} by channel groups ({gpr} groups per rank) + NCCL all-reduce of y in "
+                    f"{chunks} token chunks overlapping the down projection, {args.sm_margin} SMs "
+                    "left to the collective"),
                    "l2": "inputs larger than L2 (x 64 MiB + weights 336 MiB + h 224 MiB per step)",
                    "seed": SEED},
         "roofline": {"kernel": "gemm_mn_pair_kernel (fused gate/up + SwiGLU, CTA pairs)", "bound": "tensor",
@@ -440,6 +457,8 @@ def main():
                      "traffic_source": "ncu capture of one launch at this size, see profiles/",
                      "algorithmic_flops_per_launch": flops_mn},
         "kernels": {"gemm_mn_ms": k_mn, "gemm_k_ms": k_k,
+                    "gemm_k_ms_covers": ("down projection + barrier + reduce/gather + barrier" if fused
+                                         else "down projection"),
                     "gemm_k_algorithmic_tflops": flops_k / (k_k * 1e-3) / 1e12,
                     "gemm_k_executed_tflops": 2.0 * flops_k / (k_k * 1e-3) / 1e12,
                     "other_ms": ms_step - k_mn - k_k},

@@ -38,6 +38,8 @@ struct KPairParams {
     KParams k;
     int64_t nwin;       // 128-token windows
     int pair_tiles;     // ceil(nwin / 2) * n_chunks
+    int pair_windows;   // ceil(nwin / 2)
+    int window_shift;   // peer output: the walk over the pair windows starts here (and wraps)
 };
 
 template <bool kBf16, bool kPeer>
@@ -98,9 +100,15 @@ gemm_k_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         for (int w = 0; w < p.words; ++w) any |= pair_word(pw, w);
         return any != 0;
     };
+    // Peer output: rank r starts its walk at the windows owned by rank r + 1, so that at any
+    // moment the ranks store into different owners instead of all into the same one.
     auto decode = [&](int tile, int& pw, int& nchunk) {
         pw = tile / p.n_chunks;
         nchunk = tile - pw * p.n_chunks;
+        if constexpr (kPeer) {
+            pw += pp.window_shift;
+            if (pw >= pp.pair_windows) pw -= pp.pair_windows;
+        }
     };
 
     if (warp < 4) {
@@ -361,7 +369,12 @@ int gemm_k_pair_launch(const void* A, int64_t lda, const void* W, int64_t ldw, K
     pp.k.ksplit = 1;
     pp.k.acc32 = nullptr;
     pp.nwin = (p.M + kBM - 1) / kBM;
-    pp.pair_tiles = static_cast<int>((pp.nwin + 1) / 2) * pp.k.n_chunks;
+    pp.pair_windows = static_cast<int>((pp.nwin + 1) / 2);
+    pp.pair_tiles = pp.pair_windows * pp.k.n_chunks;
+    pp.window_shift = 0;
+    if (p.world > 1)
+        pp.window_shift = static_cast<int>((int64_t((p.my_rank + 1) % p.world) * p.rows_per_owner / (2 * kBM)) %
+                                           pp.pair_windows);
     if (2 * pp.pair_tiles < grid) grid = 2 * pp.pair_tiles;
     auto launch = [&](auto kernel, size_t smem_bytes) -> int {
         DPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -19,7 +19,7 @@ constexpr int kMaxPeersRG = 8;
 struct ReduceGatherParams {
     const uint8_t* stage;            // [world, rows_per_owner, ld] halves (this rank's staging)
     const uint8_t* residual;         // [M, ld] halves or NULL (local)
-    uint8_t* out[kMaxPeersRG];       // every rank's [M, ld] output
+    uint8_t* out[kMaxPeersRG];       // every rank's [M, ld] output, starting with rank + 1
     int world, rank;
     int64_t rows_per_owner, rows;    // rows = owned rows inside the token range
     int64_t ld;
@@ -51,23 +51,31 @@ __global__ void __launch_bounds__(256) reduce_gather_kernel(const ReduceGatherPa
         const int64_t r = i / chunks_per_row;
         const int64_t c = i - r * chunks_per_row;
         const int64_t off = (r * p.ld + c * 8) * 2;
+        // all slabs are requested before the first is used
+        uint4 v[kMaxPeersRG];
+#pragma unroll
+        for (int j = 0; j < kMaxPeersRG; ++j)
+            if (j < p.world) v[j] = *reinterpret_cast<const uint4*>(p.stage + j * slab + off);
+        const int64_t goff = ((first_row + r) * p.ld + c * 8) * 2;
+        uint4 res = make_uint4(0, 0, 0, 0);
+        if (p.residual) res = *reinterpret_cast<const uint4*>(p.residual + goff);
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         // the slabs are summed in rank order on every owner: the result does not depend on
         // which rank computes it
-        for (int j = 0; j < p.world; ++j)
-            accumulate8<kBf16>(acc, *reinterpret_cast<const uint4*>(p.stage + j * slab + off));
-        const int64_t goff = ((first_row + r) * p.ld + c * 8) * 2;
-        if (p.residual) accumulate8<kBf16>(acc, *reinterpret_cast<const uint4*>(p.residual + goff));
+#pragma unroll
+        for (int j = 0; j < kMaxPeersRG; ++j)
+            if (j < p.world) accumulate8<kBf16>(acc, v[j]);
+        if (p.residual) accumulate8<kBf16>(acc, res);
         uint4 o;
         o.x = pack_half2<kBf16>(acc[0], acc[1]);
         o.y = pack_half2<kBf16>(acc[2], acc[3]);
         o.z = pack_half2<kBf16>(acc[4], acc[5]);
         o.w = pack_half2<kBf16>(acc[6], acc[7]);
-        for (int j = 0; j < p.world; ++j) {
-            // start with the neighbour so that the ranks do not all store to the same peer at once
-            const int dst = (p.rank + 1 + j) % p.world;
-            *reinterpret_cast<uint4*>(p.out[dst] + goff) = o;
-        }
+        // out[] starts with the next rank (rotated on the host), so that the ranks do not all
+        // store to the same peer at once
+#pragma unroll
+        for (int j = 0; j < kMaxPeersRG; ++j)
+            if (j < p.world) *reinterpret_cast<uint4*>(p.out[j] + goff) = o;
     }
 }
 
@@ -132,7 +140,7 @@ extern "C" int dpk_reduce_gather(const void* stage, void* const* out, const void
     for (int i = 0; i < kMaxPeersRG; ++i) p.out[i] = nullptr;
     for (int i = 0; i < world; ++i) {
         DPK_REQUIRE(out[i] && aligned16(out[i]), "output %d", i);
-        p.out[i] = static_cast<uint8_t*>(out[i]);
+        p.out[(i - rank - 1 + 2 * world) % world] = static_cast<uint8_t*>(out[i]);
     }
     p.world = world;
     p.rank = rank;

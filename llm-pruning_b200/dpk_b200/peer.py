@@ -85,6 +85,7 @@ class RowParallelSum:
         self.lib = N.load()
         self.code = 1 if dtype == torch.bfloat16 else 0
         self._ws = None
+        self.timers = None      # dict -> lists of CUDA events at the five points of a fused sum
 
     # ---- construction -----------------------------------------------------------------
     @staticmethod
@@ -165,11 +166,31 @@ class RowParallelSum:
 
     def gemm_k(self, A2: torch.Tensor, W: torch.Tensor, row_bits: torch.Tensor,
                win_bits: torch.Tensor, NG: int, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        self._mark("start")
         self.scatter(A2, W, row_bits, win_bits, NG)
+        self._mark("scatter")
         self._barrier()          # every rank's partial sums have landed
+        self._mark("barrier1")
         y = self.reduce(A2.shape[0], residual)
+        self._mark("reduce")
         self._barrier()          # every owner's rows have landed; staging may be reused
+        self._mark("barrier2")
         return y
+
+    def _mark(self, name: str) -> None:
+        if self.timers is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.timers.setdefault(name, []).append(ev)
+
+    def phase_ms(self) -> dict:
+        """Mean milliseconds of the four phases since ``timers`` was set to a dict."""
+        names = ["start", "scatter", "barrier1", "reduce", "barrier2"]
+        tm = self.timers or {}
+        if not tm.get("start"):
+            return {}
+        return {b + "_ms": sum(e0.elapsed_time(e1) for e0, e1 in zip(tm[a], tm[b])) / len(tm[a])
+                for a, b in zip(names[:-1], names[1:])}
 
     def routed_gemm_k(self, A: torch.Tensor, W: torch.Tensor, Mask: torch.Tensor,
                       residual: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -130,6 +130,16 @@ def main(argv=None):
     ms = tried[best]
     chunks, margin = (int(v) for v in best.split(":"))
 
+    fused_phases = None
+    if fused:
+        layer.sum_o.timers, layer.ffn.row_parallel.timers = {}, {}
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        fused_phases = {"o_projection": layer.sum_o.phase_ms(),
+                        "down_projection": layer.ffn.row_parallel.phase_ms()}
+        layer.sum_o.timers, layer.ffn.row_parallel.timers = None, None
+
     # phase split: the unpipelined schedule, one phase after the other
     _native.check(lib.dpk_set_sm_margin(0))
     layer.token_chunks = 1
@@ -192,6 +202,7 @@ def main(argv=None):
                 f"2 NCCL all-reduces of [T,H] bf16, {chunks} token chunks pipelined, {margin} SMs "
                 "left to the collective"),
             "ms_per_layer_with_nccl_all_reduce": nccl_ms,
+            "fused_sum_phases_ms": fused_phases,
             "ms_per_layer": ms, "tokens_per_s": T / (ms * 1e-3),
             "settings_ms (chunks:sm_margin)": tried,
             "phases_unpipelined": phases,
