@@ -61,7 +61,7 @@ const char* dpk_last_error(void);
  * filled / drained, 103/104 the same for an accumulator in tensor memory, 105 a routing
  * index outside the token range, 106 misaligned shared memory; kernel 1 gemm_mn, 2 gemm_mn
  * on CTA pairs, 3 gemm_k, 4 gemm_k on CTA pairs, 5 prefill attention, 6 decode attention,
- * 7 routing.  The first report wins until it is read.
+ * 7 routing, 9 router + norm.  The first report wins until it is read.
  * The reference's device code has no counterpart: its waits are unbounded
  * (DynamicPruningKernels/include/attention_prefill/v3/sm12x_causal.cuh:401,535).
  */
@@ -255,6 +255,25 @@ size_t dpk_attn_decode_workspace_bytes(int B, int Tk, int Hq, int Hk, int D, int
 int dpk_attn_decode(const void* Q, const void* K, const void* V, const uint8_t* mask,
                     const uint32_t* leftpad, void* O, int B, int Tk, int Hq, int Hk, int D, int NG,
                     float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Token router fused with the RMSNorm that reads the same hidden state (reference:
+ * TokenRouter.forward, WIDE/wrapper/base_layer.py:89-114 -- the arithmetic of BottleneckRouter,
+ * PruningInferSim/ops/router.py:85-126 --, the evaluation-time decision of
+ * base_layer.py:204-207, and the norm modules called beside it,
+ * WIDE/wrapper/attn_group_ffn_block.py:170-176, 195-200):
+ *   c = x . w_down^T + b_down  [R];  logits = c . w_route^T + b_route  [NG,2];
+ *   execute[m,g] = logits[m,g,0] >= logits[m,g,1]  (argmax of the pair, ties execute);
+ *   xn = gamma * dtype(x * rsqrt(mean(x^2) + eps))  when gamma and xn are given.
+ * x [M,ldx], w_down [R,H], w_route [2*NG,R] (contiguous), biases optional, execute [M,NG]
+ * bytes, logits optional fp32 [M,NG,2].  R <= 16, H a multiple of 32 and at most ~14000.
+ * round_like_module != 0 rounds c and the logits to `dtype` as a module running in that
+ * dtype does; 0 keeps fp32.  x is read from device memory once.
+ */
+int dpk_router_norm(const void* x, int64_t ldx, const void* gamma, float eps, const void* w_down,
+                    const void* b_down, const void* w_route, const void* b_route, void* xn,
+                    int64_t ldxn, uint8_t* execute, float* logits, int64_t M, int H, int R, int NG,
+                    int dtype, int round_like_module, void* stream);
 
 /* ---- tensor parallel: the row-parallel sum fused into the projection ---------------
  *

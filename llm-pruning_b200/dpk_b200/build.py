@@ -36,6 +36,7 @@ SOURCES = [
     "dpk_attn_prefill_tc.cu",
     "dpk_attn_decode.cu",
     "dpk_peer.cu",
+    "dpk_router_norm.cu",
 ]
 
 NVCC_FLAGS = [

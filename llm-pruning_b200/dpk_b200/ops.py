@@ -73,6 +73,46 @@ def topk_route_mask(logits: torch.Tensor, keep: int) -> torch.Tensor:
     return mask.view(torch.bool)
 
 
+def router_norm(x: torch.Tensor, w_down: torch.Tensor, b_down: Optional[torch.Tensor],
+                w_route: torch.Tensor, b_route: Optional[torch.Tensor],
+                norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                return_logits: bool = False, round_like_module: bool = True):
+    """Two-stage token router, its evaluation-time decision and (optionally) the RMSNorm of
+    the same hidden state, in one pass over ``x [..., H]``.
+
+    Mirrors ``TokenRouter.forward`` followed by the eval branch of ``_gumbel_softmax``
+    (``WIDE/wrapper/base_layer.py:89-114, 204-207``) and the layer norm called next to it
+    (``WIDE/wrapper/attn_group_ffn_block.py:170-176``).  Returns ``(execute bool [..., NG],
+    xn [..., H] or None, logits float32 [..., NG, 2] or None)``."""
+    dev = _need_cuda(x, w_down, w_route, b_down, b_route, norm_weight)
+    code = _dtype_code(x)
+    lead, H = x.shape[:-1], x.shape[-1]
+    x2 = x.reshape(-1, H)
+    if x2.stride(-1) != 1 or x2.stride(0) % 8:
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    R = w_down.shape[0]
+    if w_down.shape != (R, H) or w_route.shape[1] != R or w_route.shape[0] % 2:
+        raise ValueError("w_down must be [R,H] and w_route [2*NG,R]")
+    NG = w_route.shape[0] // 2
+    for t in (w_down, w_route, b_down, b_route, norm_weight):
+        if t is not None and t.dtype != x.dtype:
+            raise ValueError("router and norm parameters must have the dtype of x")
+    wd, wr = w_down.contiguous(), w_route.contiguous()
+    execute = torch.empty((M, NG), dtype=torch.uint8, device=dev)
+    xn = torch.empty((M, H), dtype=x.dtype, device=dev) if norm_weight is not None else None
+    logits = torch.empty((M, NG, 2), dtype=torch.float32, device=dev) if return_logits else None
+    with torch.cuda.device(dev):
+        N.check(N.load().dpk_router_norm(
+            x2.data_ptr(), x2.stride(0), _ptr(norm_weight.contiguous() if norm_weight is not None else None),
+            float(eps), wd.data_ptr(), _ptr(b_down.contiguous() if b_down is not None else None),
+            wr.data_ptr(), _ptr(b_route.contiguous() if b_route is not None else None), _ptr(xn), H,
+            execute.data_ptr(), _ptr(logits), M, H, R, NG, code, 1 if round_like_module else 0,
+            _stream()))
+    return (execute.view(*lead, NG).bool(), xn.view(*lead, H) if xn is not None else None,
+            logits.view(*lead, NG, 2) if logits is not None else None)
+
+
 def route_compact(mask: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Routing layout of a ``[M,NG]`` or ``[B,M,NG]`` mask (sorted per batch).
 

@@ -201,11 +201,51 @@ def run_gemm(args, which):
             "dense_ms": dms, "speedup_vs_dense": dms / kms, "speedup_vs_dense_through_api": dms / ms}
 
 
+def run_router_norm(args):
+    """Router + RMSNorm in front of the config-5 layer: H=8192, 224 FFN groups, rank 16."""
+    M, H, NG, R = args.tokens or 16384, args.hidden or 8192, 224, 16
+    gen = torch.Generator(device="cuda").manual_seed(SEED)
+    bf = torch.bfloat16
+    x = torch.randn(M, H, generator=gen, device="cuda").to(bf)
+    gamma = (1.0 + 0.1 * torch.randn(H, generator=gen, device="cuda")).to(bf)
+    wd = (torch.randn(R, H, generator=gen, device="cuda") / H ** 0.5).to(bf)
+    bd = (0.1 * torch.randn(R, generator=gen, device="cuda")).to(bf)
+    wr = (torch.randn(2 * NG, R, generator=gen, device="cuda") / R ** 0.5).to(bf)
+    br = (0.1 * torch.randn(2 * NG, generator=gen, device="cuda")).to(bf)
+    # ten calls per sample: the kernel is short enough for the host-side work of one call (output
+    # allocation, argument marshalling) to show up between two events otherwise
+    def ten():
+        for _ in range(10):
+            ops.router_norm(x, wd, bd, wr, br, norm_weight=gamma, eps=1e-5)
+    ms, lo, hi = (t / 10 for t in time_ms(ten, args.reps))
+
+    def torch_equivalent():
+        xf = x.float()
+        xn = gamma * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).to(bf)
+        logits = torch.nn.functional.linear(torch.nn.functional.linear(x, wd, bd), wr, br)
+        return xn, logits.view(M, NG, 2).argmax(-1).bool().logical_not()
+
+    def ten_torch():
+        for _ in range(10):
+            torch_equivalent()
+    dms = time_ms(ten_torch, args.reps)[0] / 10
+    nbytes = 2.0 * M * H * 2 + M * NG            # x read once, xn written once, decisions
+    _, peak_gbs, src = peaks()
+    ach = nbytes / (ms * 1e-3) / 1e9
+    return {"kernel": "router_norm", "workload": f"M={M} H={H} NG={NG} rank={R}, RMSNorm output + "
+            "decisions (x 256 MiB > L2)", "ms": ms, "ms_q20": lo, "ms_q80": hi,
+            "algorithmic_bytes": nbytes,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak_gbs, "unit": "GB/s",
+                         "frac": ach / peak_gbs, "peak_source": src + " copy bandwidth"},
+            "torch_ms": dms, "speedup_vs_torch": dms / ms}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--kernel", required=True,
                     choices=["attention_prefill", "attention_decode", "ffn", "ffn_decode",
-                             "gemm_mn", "gemm_k"])
+                             "gemm_mn", "gemm_k", "router_norm"])
+    ap.add_argument("--hidden", type=int, default=0, help="override the hidden size (router_norm)")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--tokens", type=int, default=0, help="override the token / KV length")
     ap.add_argument("--batch", type=int, default=0, help="override the decode batch")
@@ -219,6 +259,8 @@ def main(argv=None):
         res = run_ffn(args)
     elif args.kernel == "ffn_decode":
         res = run_ffn(args, decode=True)
+    elif args.kernel == "router_norm":
+        res = run_router_norm(args)
     else:
         res = run_gemm(args, args.kernel)
     status = ops.device_status()

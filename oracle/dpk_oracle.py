@@ -30,6 +30,8 @@ __all__ = [
     "as_group_mask",
     "topk_route_mask",
     "route_compact",
+    "bottleneck_router",
+    "rms_norm",
     "gemm_mn",
     "gemm_k",
     "ffn_swiglu",
@@ -75,6 +77,55 @@ def topk_route_mask(logits: torch.Tensor, keep: int) -> torch.Tensor:
     mask = torch.zeros(l32.shape, dtype=torch.bool)
     mask.scatter_(-1, order[..., :keep], True)
     return mask
+
+
+def _round_to(t: torch.Tensor, dtype: Optional[torch.dtype]) -> torch.Tensor:
+    return t if dtype is None else t.to(dtype).to(torch.float32)
+
+
+def bottleneck_router(x: torch.Tensor, w_down: torch.Tensor, b_down: Optional[torch.Tensor],
+                      w_route: torch.Tensor, b_route: Optional[torch.Tensor],
+                      module_dtype: Optional[torch.dtype] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Two-stage token router and its evaluation-time decision.
+
+    ``logits = (x @ w_down.T + b_down) @ w_route.T + b_route`` reshaped to ``[..., NG, 2]``
+    (``WIDE/wrapper/base_layer.py:89-114`` ``TokenRouter``; the same arithmetic as
+    ``PruningInferSim/ops/router.py:85-126`` ``BottleneckRouter``).  A group is executed
+    when the argmax over the pair is index 0 -- ``skip = argmax(-1).bool(); execute = ~skip``
+    (``base_layer.py:204-207``) -- and ``argmax`` returns the first index on a tie, so
+    ``execute = logits[..., 0] >= logits[..., 1]``.
+
+    ``module_dtype`` (bf16 / fp16) reproduces the rounding of a module that runs in that
+    dtype: the output of each ``nn.Linear`` is rounded once (fp32 accumulation, bias added
+    before the rounding).  ``None`` keeps everything in fp32.
+    Returns ``(logits float32 [..., NG, 2], execute bool [..., NG])``.
+    """
+    xf = x.to(torch.float32)
+    c = xf @ w_down.to(torch.float32).T
+    if b_down is not None:
+        c = c + b_down.to(torch.float32)
+    c = _round_to(c, module_dtype)
+    l = c @ w_route.to(torch.float32).T
+    if b_route is not None:
+        l = l + b_route.to(torch.float32)
+    l = _round_to(l, module_dtype)
+    if l.shape[-1] % 2:
+        raise ValueError("the router must produce two logits per group")
+    l = l.reshape(*l.shape[:-1], l.shape[-1] // 2, 2)
+    return l, l[..., 0] >= l[..., 1]
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm as the wrapped decoder layers apply it (``input_layernorm`` /
+    ``post_attention_layernorm``, ``WIDE/wrapper/attn_group_ffn_block.py:170,195``; the
+    modules are the Hugging Face ``LlamaRMSNorm`` of transformers 5.5, a third-party
+    dependency of the reference): statistics in fp32, the normalised value rounded to the
+    input dtype, then multiplied by the weight in that dtype."""
+    dt = x.dtype
+    xf = x.to(torch.float32)
+    var = xf.pow(2).mean(-1, keepdim=True)
+    y = (xf * torch.rsqrt(var + eps)).to(dt)
+    return weight.to(dt) * y
 
 
 def route_compact(mask2d: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:

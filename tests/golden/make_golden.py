@@ -162,6 +162,52 @@ def main(root: str) -> None:
          out_ng16_leftpad=run("attention_decode", q, k, v, m16, backend="torch",
                               Leftpad=lp, is_causal=False))
 
+    router_fixture(root)
+
+
+def router_fixture(root: str) -> None:
+    """The reference's ``TokenRouter`` (``WIDE/wrapper/base_layer.py:89-114``) with its
+    evaluation-time decision (``:204-207``) and the ``LlamaRMSNorm`` its layers wrap.
+    ``base_layer`` imports two optional packages that this container lacks (peft, liger
+    kernels) for classes the router does not use; they are stubbed for the import."""
+    from unittest import mock
+    for name in ("peft", "peft.tuners", "peft.tuners.lora", "liger_kernel", "liger_kernel.ops",
+                 "liger_kernel.ops.swiglu"):
+        sys.modules.setdefault(name, mock.MagicMock())
+    sys.path.insert(0, os.path.join(root, "WIDE"))
+    from wrapper.base_layer import TokenRouter
+    from transformers.models.llama.modeling_llama import LlamaRMSNorm
+
+    torch.manual_seed(23)
+    B, T, H, NG, R = 2, 45, 256, 12, 16
+    router = TokenRouter(H, group_num=NG, rank_size=R).eval()
+    with torch.no_grad():
+        for lin in (router.compressor, router.router):      # bf16-exact weights, non-zero biases
+            lin.weight.copy_(bf16_round(lin.weight))
+            lin.bias.copy_(bf16_round(torch.randn_like(lin.bias) * 0.1))
+    norm = LlamaRMSNorm(H, eps=1e-5)
+    with torch.no_grad():
+        norm.weight.copy_(bf16_round(1.0 + 0.1 * torch.randn(H)))
+    x = bf16_round(torch.randn(B, T, H) * 1.5)
+    with torch.no_grad():
+        logits32 = router(x)                                 # [B,T,NG,2], fp32 module
+        skip = logits32.argmax(dim=-1).to(torch.bool)        # base_layer.py:205
+        execute32 = skip.logical_not()
+        r16 = TokenRouter(H, group_num=NG, rank_size=R).eval()
+        r16.load_state_dict(router.state_dict())
+        r16 = r16.to(torch.bfloat16)
+        logits16 = r16(x.to(torch.bfloat16))
+        execute16 = logits16.argmax(dim=-1).to(torch.bool).logical_not()
+        xn16 = norm.to(torch.bfloat16)(x.to(torch.bfloat16))
+    save("router_norm", x=x, w_down=router.compressor.weight.detach(),
+         b_down=router.compressor.bias.detach(), w_route=router.router.weight.detach(),
+         b_route=router.router.bias.detach(), gamma=norm.weight.detach().float(),
+         eps=np.float32(1e-5), logits_fp32=logits32, execute_fp32=execute32.numpy(),
+         logits_bf16=logits16.float(), execute_bf16=execute16.numpy(), xn_bf16=xn16.float())
+
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) > 2 and sys.argv[2] == "router":
+        router_fixture(sys.argv[1])
+    else:
+        main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -751,3 +751,65 @@ def test_row_parallel_sum_emulated_ranks(ops, world, M, N, Kl, NGl):
             assert_rel(outs[r], expect, tol=3e-2)
         for r in range(1, world):            # and the ranks agree bit for bit
             assert torch.equal(outs[r], outs[0])
+
+
+def test_router_norm_golden_fixture(ops):
+    """The reference's TokenRouter (bf16 module and fp32 module) and LlamaRMSNorm outputs."""
+    z = golden_io.load("router_norm")
+    bf = torch.bfloat16
+    x = dev(z["x"], bf)
+    par = [dev(z[k], bf) for k in ("w_down", "b_down", "w_route", "b_route")]
+    execute, xn, logits = ops.router_norm(x, *par, norm_weight=dev(z["gamma"], bf), eps=float(z["eps"]),
+                                          return_logits=True)
+    l16 = z["logits_bf16"]
+    torch.testing.assert_close(logits.cpu(), l16, rtol=2e-2, atol=2e-2)
+    assert (logits.cpu() == l16).float().mean() > 0.95
+    clear = (l16[..., 0] - l16[..., 1]).abs() > 4e-2
+    assert torch.equal(execute.cpu()[clear], z["execute_bf16"][clear])
+    # decisions follow the kernel's own logits exactly (integer step: bit-exact)
+    assert torch.equal(execute.cpu(), logits.cpu()[..., 0] >= logits.cpu()[..., 1])
+    # RMSNorm: statistics in fp32, two roundings -- at most one bf16 ulp from the module
+    want = z["xn_bf16"]
+    got = xn.float().cpu()
+    assert (got == want).float().mean() > 0.99
+    assert ((got - want).abs() <= want.abs() * 2 ** -6 + 1e-30).all()
+    # fp32 logits without the module roundings
+    execute32, none, logits32 = ops.router_norm(x, *par, return_logits=True, round_like_module=False)
+    assert none is None
+    torch.testing.assert_close(logits32.cpu(), z["logits_fp32"], rtol=1e-4, atol=1e-4)
+    clear32 = (z["logits_fp32"][..., 0] - z["logits_fp32"][..., 1]).abs() > 1e-3
+    assert torch.equal(execute32.cpu()[clear32], z["execute_fp32"][clear32])
+
+
+@pytest.mark.parametrize("M,H,NG,R,dtype,biases", [(1000, 4096, 112, 16, torch.bfloat16, True),
+                                                   (301, 8192, 224, 16, torch.bfloat16, True),
+                                                   (77, 1024, 8, 16, torch.float16, True),
+                                                   (64, 512, 300, 8, torch.bfloat16, False),
+                                                   (5, 2048, 1, 3, torch.bfloat16, False)])
+def test_router_norm_against_oracle(ops, M, H, NG, R, dtype, biases):
+    """Ragged last tile, more groups than threads, router ranks below 16, fp16, no biases."""
+    g = seeded(M + H)
+    def rnd(*shape, std=1.0):
+        return (torch.randn(*shape, generator=g) * std).to(dtype).float()
+    x = rnd(2, M, H, std=1.3) if M % 2 else rnd(M, H, std=1.3)
+    wd, wr = rnd(R, H, std=H ** -0.5), rnd(2 * NG, R, std=R ** -0.5)
+    bd, br = (rnd(R, std=0.1), rnd(2 * NG, std=0.1)) if biases else (None, None)
+    gamma = (1.0 + 0.1 * torch.randn(H, generator=g)).to(dtype).float()
+    d = lambda t: None if t is None else dev(t, dtype)
+    execute, xn, logits = ops.router_norm(d(x), d(wd), d(bd), d(wr), d(br), norm_weight=d(gamma),
+                                          eps=1e-6, return_logits=True)
+    want_l, want_e = O.bottleneck_router(x, wd, bd, wr, br, module_dtype=dtype)
+    got_l = logits.cpu()
+    assert got_l.shape == want_l.shape and execute.shape == want_e.shape
+    # a one-ulp difference of the rounded hidden vector moves a logit by a few of its own ulps
+    torch.testing.assert_close(got_l, want_l, rtol=3e-2, atol=3e-2)
+    assert (got_l == want_l).float().mean() > 0.9
+    assert torch.equal(execute.cpu(), got_l[..., 0] >= got_l[..., 1])
+    clear = (want_l[..., 0] - want_l[..., 1]).abs() > 6e-2
+    assert torch.equal(execute.cpu()[clear], want_e[clear])
+    want_x = O.rms_norm(x.to(dtype), gamma, 1e-6).float()
+    got_x = xn.float().cpu()
+    assert (got_x == want_x).float().mean() > 0.99
+    # two roundings in a row: a one-ulp difference of the first can grow to two in the product
+    ulp = 2 ** -6 if dtype == torch.bfloat16 else 2 ** -9
+    assert ((got_x - want_x).abs() <= want_x.abs() * ulp + 1e-6).all()

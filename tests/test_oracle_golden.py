@@ -90,3 +90,35 @@ def test_decode_attention():
     torch.testing.assert_close(O.attention_decode(q, k, v, z["mask8"]), z["out_ng8"], **TIGHT)
     torch.testing.assert_close(O.attention_decode(q, k, v, z["mask16"], leftpad=z["leftpad"]),
                                z["out_ng16_leftpad"], **TIGHT)
+
+
+def test_bottleneck_router_and_rms_norm():
+    """Against the reference's own TokenRouter (fp32 and bf16 module) and LlamaRMSNorm."""
+    z = golden_io.load("router_norm")
+    x = z["x"]
+    args = (z["w_down"], z["b_down"], z["w_route"], z["b_route"])
+    logits, execute = O.bottleneck_router(x, *args)
+    torch.testing.assert_close(logits, z["logits_fp32"], rtol=1e-5, atol=1e-5)
+    # decisions: identical wherever the pair is not within fp32 rounding of a tie
+    margin = (z["logits_fp32"][..., 0] - z["logits_fp32"][..., 1]).abs()
+    clear = margin > 1e-5
+    assert clear.float().mean() > 0.99
+    assert torch.equal(execute[clear], z["execute_fp32"][clear])
+    # module in bf16: each Linear's output is rounded once
+    logits16, execute16 = O.bottleneck_router(x, *args, module_dtype=torch.bfloat16)
+    l16 = z["logits_bf16"]
+    # the hidden 16-vector sits on bf16 rounding boundaries now and then: one ulp of it moves a
+    # logit by a few bf16 ulps, so compare with that slack and the decisions where clear
+    torch.testing.assert_close(logits16, l16, rtol=2e-2, atol=2e-2)
+    assert (logits16 == l16).float().mean() > 0.95
+    clear16 = (l16[..., 0] - l16[..., 1]).abs() > 4e-2
+    assert torch.equal(execute16[clear16], z["execute_bf16"][clear16])
+    assert (execute16 == z["execute_bf16"]).float().mean() > 0.98
+    # ties go to "execute" (argmax returns the first index)
+    tie = torch.zeros(1, 1, 16)
+    _, ex = O.bottleneck_router(tie, torch.zeros(16, 16), None, torch.zeros(4, 16), None)
+    assert ex.all()
+    # RMSNorm in bf16
+    xn = O.rms_norm(x.to(torch.bfloat16), z["gamma"], float(z["eps"]))
+    assert xn.dtype == torch.bfloat16
+    assert torch.equal(xn.float(), z["xn_bf16"])
