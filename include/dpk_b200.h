@@ -275,6 +275,20 @@ int dpk_router_norm(const void* x, int64_t ldx, const void* gamma, float eps, co
                     int64_t ldxn, uint8_t* execute, float* logits, int64_t M, int H, int R, int NG,
                     int dtype, int round_like_module, void* stream);
 
+/*
+ * Rotary embedding of q and k fused with the append of k and v to a preallocated
+ * sequence-first KV cache (reference: apply_rotary_pos_emb, WIDE/wrapper/base_layer.py:18-44,
+ * then past_key_values.update, WIDE/wrapper/attn_group_ffn_block.py:62-67, whose layer
+ * concatenates [B,T,Hk,D] tensors, WIDE/wrapper/cache.py:24-46).
+ *   q [B,T,Hq,D] rotated in place; k [B,T,Hk,D]; v [B,T,Hk,D]; cos, sin [T,D] (batch stride
+ *   0) or [B,T,D]; k_cache, v_cache [B,capacity,Hk,D]: rows past_len .. past_len+T-1 receive
+ *   the rotated k and v.  Without caches (both NULL) k is rotated in place.
+ * fp32 arithmetic, one rounding.  D a multiple of 16.
+ */
+int dpk_rope_append(void* q, void* k, const void* v, const void* cos, const void* sin,
+                    int64_t cs_batch_stride, void* k_cache, void* v_cache, int B, int T, int Hq,
+                    int Hk, int D, int64_t capacity, int64_t past_len, int dtype, void* stream);
+
 /* ---- tensor parallel: the row-parallel sum fused into the projection ---------------
  *
  * The reference runs one process on one GPU and has no collective; it only sketches the

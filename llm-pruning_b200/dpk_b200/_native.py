@@ -49,6 +49,8 @@ SIGNATURES = {
                                _f32, _i32, _vp, _sz, _vp]),
     "dpk_router_norm": (_i32, [_vp, _i64, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64,
                                _i32, _i32, _i32, _i32, _i32, _vp]),
+    "dpk_rope_append": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _i32,
+                               _i64, _i64, _i32, _vp]),
     "dpk_peer_alloc": (_i32, [_sz, C.POINTER(_vp), _vp]),
     "dpk_peer_open": (_i32, [_vp, C.POINTER(_vp)]),
     "dpk_peer_close": (_i32, [_vp]),

@@ -37,6 +37,7 @@ SOURCES = [
     "dpk_attn_decode.cu",
     "dpk_peer.cu",
     "dpk_router_norm.cu",
+    "dpk_rope.cu",
 ]
 
 NVCC_FLAGS = [

@@ -113,6 +113,49 @@ def router_norm(x: torch.Tensor, w_down: torch.Tensor, b_down: Optional[torch.Te
             logits.view(*lead, NG, 2) if logits is not None else None)
 
 
+def rope_append(q: torch.Tensor, k: torch.Tensor, v: Optional[torch.Tensor], cos: torch.Tensor,
+                sin: torch.Tensor, k_cache: Optional[torch.Tensor] = None,
+                v_cache: Optional[torch.Tensor] = None, past_len: int = 0):
+    """Rotary embedding of ``q [B,T,Hq,D]`` and ``k [B,T,Hk,D]`` (in place) and, when the
+    caches ``[B,capacity,Hk,D]`` are given, the append of the rotated ``k`` and of ``v`` at
+    ``past_len``.  ``cos, sin``: ``[T,D]``, ``[1,T,D]`` or ``[B,T,D]``.  Mirrors
+    ``apply_rotary_pos_emb`` + ``past_key_values.update`` of the reference's attention wrapper
+    (``WIDE/wrapper/attn_group_ffn_block.py:60-67``).  Returns ``(q, keys, values)`` where
+    ``keys, values`` are the first ``past_len+T`` cache rows (or ``k, v`` without a cache)."""
+    dev = _need_cuda(q, k, v, cos, sin, k_cache, v_cache)
+    code = _dtype_code(q)
+    B, T, Hq, D = q.shape
+    Hk = k.shape[2]
+    if k.shape != (B, T, Hk, D) or (v is not None and v.shape != k.shape):
+        raise ValueError("q, k, v must be [B,T,heads,D] with equal B, T, D")
+    if not (q.is_contiguous() and k.is_contiguous() and (v is None or v.is_contiguous())):
+        raise ValueError("q, k, v must be contiguous (q and k are rotated in place)")
+    if cos.dim() == 2:
+        cos, sin = cos[None], sin[None]
+    if cos.shape[-2:] != (T, D) or sin.shape != cos.shape or cos.shape[0] not in (1, B):
+        raise ValueError("cos and sin must be [T,D], [1,T,D] or [B,T,D]")
+    cos, sin = cos.contiguous(), sin.contiguous()
+    if cos.dtype != q.dtype or sin.dtype != q.dtype or k.dtype != q.dtype:
+        raise ValueError("q, k, cos and sin must share one dtype")
+    stride = 0 if cos.shape[0] == 1 else T * D
+    capacity = 0
+    if k_cache is not None:
+        if v_cache is None or v is None:
+            raise ValueError("k_cache needs v_cache and v")
+        capacity = k_cache.shape[1]
+        want = (B, capacity, Hk, D)
+        if k_cache.shape != want or v_cache.shape != want or not (
+                k_cache.is_contiguous() and v_cache.is_contiguous()):
+            raise ValueError("caches must be contiguous [B,capacity,Hk,D]")
+    with torch.cuda.device(dev):
+        N.check(N.load().dpk_rope_append(q.data_ptr(), k.data_ptr(), _ptr(v), cos.data_ptr(),
+                                         sin.data_ptr(), stride, _ptr(k_cache), _ptr(v_cache), B, T,
+                                         Hq, Hk, D, capacity, past_len, code, _stream()))
+    if k_cache is None:
+        return q, k, v
+    return q, k_cache[:, :past_len + T], v_cache[:, :past_len + T]
+
+
 def route_compact(mask: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Routing layout of a ``[M,NG]`` or ``[B,M,NG]`` mask (sorted per batch).
 

@@ -132,3 +132,60 @@ def routed_o_proj(attn_output: torch.Tensor, o_weight: torch.Tensor, execute_att
     flat = attn_output.reshape(b, s, -1)
     mask = as_bool_mask(execute_attn, b, s, execute_attn.shape[-1], attn_output.device)
     return ops.gemm_k(flat, o_weight, mask, **(metadata or {}))
+
+
+class RoutedTokenRouter(nn.Module):
+    """``TokenRouter`` (``WIDE/wrapper/base_layer.py:89-114``) with the evaluation-time decision
+    of ``WrapperDecoderLayer._gumbel_softmax`` (``:204-207``) computed by one kernel.
+
+    Parameter names follow the reference module (``compressor``, ``router``), so its state dict
+    loads unchanged.  ``decide`` returns what the layer derives from the router at inference --
+    ``execute`` / ``skip`` as 0/1 tensors in the activation dtype, ``[B,S,group_num]`` -- and,
+    when the layer norm that reads the same hidden state is passed, its output as well
+    (``WIDE/wrapper/attn_group_ffn_block.py:170-176``: ``input_layernorm(hidden_states)`` next
+    to ``router_attention(residual)``)."""
+
+    def __init__(self, hidden_size: int, group_num: int, rank_size: int = 16):
+        super().__init__()
+        if group_num <= 0 or not 0 < rank_size <= 16:
+            raise ValueError("group_num must be positive and rank_size in 1..16")
+        self.compressor = nn.Linear(hidden_size, rank_size)
+        self.router = nn.Linear(rank_size, group_num * 2)
+        self.group_num = group_num
+
+    def decide(self, hidden_states: torch.Tensor, norm: Optional[nn.Module] = None):
+        """``norm``: an RMSNorm module with ``weight`` and ``variance_epsilon`` (or ``eps``)."""
+        weight = eps = None
+        if norm is not None:
+            weight = norm.weight
+            eps = getattr(norm, "variance_epsilon", getattr(norm, "eps", 1e-6))
+        execute, normed, _ = ops.router_norm(
+            hidden_states, self.compressor.weight, self.compressor.bias, self.router.weight,
+            self.router.bias, norm_weight=weight, eps=eps if eps is not None else 1e-6)
+        dt = hidden_states.dtype
+        return execute.to(dt), execute.logical_not().to(dt), normed
+
+
+class SeqFirstKVCache:
+    """Preallocated counterpart of ``DynamicLayerSeqFirstLayer`` (``WIDE/wrapper/cache.py:10-60``):
+    keys and values stay ``[B,T,Hk,D]`` but live in one ``[B,capacity,Hk,D]`` allocation per
+    tensor, and ``rope_update`` applies the rotary embedding and writes the new rows in place
+    (the reference rotates first and then concatenates, ``attn_group_ffn_block.py:60-67``)."""
+
+    def __init__(self, batch: int, capacity: int, num_kv_heads: int, head_dim: int,
+                 dtype: torch.dtype, device):
+        shape = (batch, capacity, num_kv_heads, head_dim)
+        self.keys = torch.empty(shape, dtype=dtype, device=device)
+        self.values = torch.empty(shape, dtype=dtype, device=device)
+        self.length = 0
+
+    def get_seq_length(self) -> int:
+        return self.length
+
+    def rope_update(self, query_states: torch.Tensor, key_states: torch.Tensor,
+                    value_states: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
+        """Returns ``(rotated queries, keys[:, :length], values[:, :length])``."""
+        q, keys, values = ops.rope_append(query_states, key_states, value_states, cos, sin,
+                                          self.keys, self.values, self.length)
+        self.length += key_states.shape[1]
+        return q, keys, values

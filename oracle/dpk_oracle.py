@@ -32,6 +32,8 @@ __all__ = [
     "route_compact",
     "bottleneck_router",
     "rms_norm",
+    "rope",
+    "kv_append",
     "gemm_mn",
     "gemm_k",
     "ffn_swiglu",
@@ -126,6 +128,34 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     var = xf.pow(2).mean(-1, keepdim=True)
     y = (xf * torch.rsqrt(var + eps)).to(dt)
     return weight.to(dt) * y
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding of ``x [B,T,heads,D]`` with ``cos, sin [B or 1, T, D]``:
+    ``x*cos + rotate_half(x)*sin`` with ``rotate_half(x) = cat(-x[..., D/2:], x[..., :D/2])``
+    (``WIDE/wrapper/base_layer.py:18-44``), written per half instead of through the
+    concatenation.  fp32 arithmetic; the caller rounds."""
+    xf, c, s_ = x.to(torch.float32), cos.to(torch.float32)[:, :, None, :], sin.to(torch.float32)[:, :, None, :]
+    half = x.shape[-1] // 2
+    lo, hi = xf[..., :half], xf[..., half:]
+    out = torch.empty_like(xf)
+    out[..., :half] = lo * c[..., :half] - hi * s_[..., :half]
+    out[..., half:] = hi * c[..., half:] + lo * s_[..., half:]
+    return out
+
+
+def kv_append(k_cache: torch.Tensor, v_cache: torch.Tensor, past_len: int, k: torch.Tensor,
+              v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Sequence-first KV cache update: the reference layer returns ``cat([keys, k], dim=1)``
+    and the same for the values (``WIDE/wrapper/cache.py:24-46``); with a preallocated
+    ``[B,capacity,Hk,D]`` cache that is a write of rows ``past_len .. past_len+T-1`` and a view
+    of the first ``past_len+T`` rows."""
+    T = k.shape[1]
+    if past_len + T > k_cache.shape[1]:
+        raise ValueError("cache capacity exceeded")
+    k_cache[:, past_len:past_len + T] = k
+    v_cache[:, past_len:past_len + T] = v
+    return k_cache[:, :past_len + T], v_cache[:, :past_len + T]
 
 
 def route_compact(mask2d: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:

@@ -205,6 +205,34 @@ def router_fixture(root: str) -> None:
          eps=np.float32(1e-5), logits_fp32=logits32, execute_fp32=execute32.numpy(),
          logits_bf16=logits16.float(), execute_bf16=execute16.numpy(), xn_bf16=xn16.float())
 
+    # ---- rotary embedding and the sequence-first cache (same stubs) ------------------------
+    from wrapper import base_layer
+    from wrapper.cache import DynamicLayerSeqFirstLayer
+    rope_fn = getattr(base_layer.apply_rotary_pos_emb, "_torchdynamo_orig_callable",
+                      base_layer.apply_rotary_pos_emb)       # the function under @torch.compile
+    torch.manual_seed(29)
+    B, T0, T1, Hq, Hk, D = 2, 37, 5, 8, 2, 64
+    def qkv(T):
+        return (bf16_round(torch.randn(B, T, Hq, D)), bf16_round(torch.randn(B, T, Hk, D)),
+                bf16_round(torch.randn(B, T, Hk, D)))
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.arange(T0 + T1).float()[:, None] * inv[None, :]
+    emb = torch.cat([ang, ang], dim=-1)[None]                 # [1, T0+T1, D]
+    cos, sin = bf16_round(emb.cos()), bf16_round(emb.sin())
+    q0, k0, v0 = qkv(T0)
+    q1, k1, v1 = qkv(T1)
+    layer = DynamicLayerSeqFirstLayer()
+    layer.keys = None
+    layer.values = None
+    with torch.no_grad():
+        q0r, k0r = rope_fn(q0, k0, cos[:, :T0], sin[:, :T0])
+        keys0, values0 = layer.update(k0r, v0)
+        q1r, k1r = rope_fn(q1, k1, cos[:, T0:], sin[:, T0:])
+        keys1, values1 = layer.update(k1r, v1)
+    save("rope_cache", q0=q0, k0=k0, v0=v0, q1=q1, k1=k1, v1=v1, cos=cos[0], sin=sin[0],
+         q0_rot=q0r, q1_rot=q1r, keys_after_prefill=keys0.clone(), keys_after_step=keys1,
+         values_after_step=values1)
+
 
 if __name__ == "__main__":
     if len(sys.argv) > 2 and sys.argv[2] == "router":

@@ -813,3 +813,74 @@ def test_router_norm_against_oracle(ops, M, H, NG, R, dtype, biases):
     # two roundings in a row: a one-ulp difference of the first can grow to two in the product
     ulp = 2 ** -6 if dtype == torch.bfloat16 else 2 ** -9
     assert ((got_x - want_x).abs() <= want_x.abs() * ulp + 1e-6).all()
+
+
+def test_wide_token_router_module(ops):
+    """The wrapper-side module loads the reference module's parameter names and returns the
+    layer's execute / skip tensors and the normed hidden state."""
+    from dpk_b200.wide import RoutedTokenRouter
+
+    z = golden_io.load("router_norm")
+    bf = torch.bfloat16
+    mod = RoutedTokenRouter(256, 12, 16)
+    mod.load_state_dict({"compressor.weight": z["w_down"], "compressor.bias": z["b_down"],
+                         "router.weight": z["w_route"], "router.bias": z["b_route"]})
+    mod = mod.to("cuda", bf)
+
+    class Norm(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.weight = torch.nn.Parameter(dev(z["gamma"], bf))
+            self.variance_epsilon = float(z["eps"])
+
+    execute, skip, normed = mod.decide(dev(z["x"], bf), Norm())
+    assert execute.dtype == bf and execute.shape == (2, 45, 12)
+    assert torch.equal(execute + skip, torch.ones_like(execute))
+    l16 = z["logits_bf16"]
+    clear = (l16[..., 0] - l16[..., 1]).abs() > 4e-2
+    assert torch.equal(execute.bool().cpu()[clear], z["execute_bf16"][clear])
+    assert (normed.float().cpu() == z["xn_bf16"]).float().mean() > 0.99
+
+
+def test_rope_append_golden_fixture(ops):
+    """Prefill then one decode-sized step into a preallocated cache, against the reference's
+    apply_rotary_pos_emb + cache layer (fp32 on bf16-exact inputs; the kernel rounds once)."""
+    from dpk_b200.wide import SeqFirstKVCache
+
+    z = golden_io.load("rope_cache")
+    bf = torch.bfloat16
+    B, T0, Hq, D = z["q0"].shape
+    T1, Hk = z["q1"].shape[1], z["k0"].shape[2]
+    cache = SeqFirstKVCache(B, 48, Hk, D, bf, "cuda")
+    cos, sin = dev(z["cos"], bf), dev(z["sin"], bf)
+    q0, keys, values = cache.rope_update(dev(z["q0"], bf), dev(z["k0"], bf), dev(z["v0"], bf),
+                                         cos[:T0], sin[:T0])
+    def close(got, want):      # one bf16 rounding of an fp32 value
+        got, want = got.float().cpu(), want
+        assert ((got - want).abs() <= want.abs() * 2 ** -8 + 1e-6).all()
+    close(q0, z["q0_rot"])
+    close(keys, z["keys_after_prefill"])
+    q1, keys, values = cache.rope_update(dev(z["q1"], bf), dev(z["k1"], bf), dev(z["v1"], bf),
+                                         cos[T0:][None].expand(B, T1, D), sin[T0:][None].expand(B, T1, D))
+    assert cache.get_seq_length() == T0 + T1 and keys.shape == (B, T0 + T1, Hk, D)
+    close(q1, z["q1_rot"])
+    close(keys, z["keys_after_step"])
+    assert torch.equal(values.float().cpu(), z["values_after_step"])      # a copy: bit-exact
+    with pytest.raises(ValueError):
+        cache.rope_update(dev(z["q0"], bf), dev(z["k0"], bf), dev(z["v0"], bf), cos[:T0], sin[:T0])
+
+
+def test_rope_in_place_without_cache_d128_fp16(ops):
+    g = seeded(77)
+    h = torch.float16
+    B, T, Hq, Hk, D = 1, 19, 4, 4, 128
+    q = torch.randn(B, T, Hq, D, generator=g).to(h).float()
+    k = torch.randn(B, T, Hk, D, generator=g).to(h).float()
+    ang = torch.rand(T, D, generator=g) * 6.28
+    cos, sin = ang.cos().to(h).float(), ang.sin().to(h).float()
+    qd, kd = dev(q, h), dev(k, h)
+    q2, k2, v2 = ops.rope_append(qd, kd, None, dev(cos, h), dev(sin, h))
+    assert q2.data_ptr() == qd.data_ptr() and v2 is None
+    for got, x in ((q2, q), (k2, k)):
+        want = O.rope(x, cos[None], sin[None])
+        assert ((got.float().cpu() - want).abs() <= want.abs() * 2 ** -11 + 1e-4).all()

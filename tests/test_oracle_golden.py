@@ -1,6 +1,7 @@
 """The CPU oracle against fixtures produced by the reference itself (CPU only)."""
 
 import numpy as np
+import pytest
 import torch
 
 import golden_io
@@ -122,3 +123,21 @@ def test_bottleneck_router_and_rms_norm():
     xn = O.rms_norm(x.to(torch.bfloat16), z["gamma"], float(z["eps"]))
     assert xn.dtype == torch.bfloat16
     assert torch.equal(xn.float(), z["xn_bf16"])
+
+
+def test_rope_and_cache_append():
+    """Against the reference's apply_rotary_pos_emb and its sequence-first cache layer."""
+    z = golden_io.load("rope_cache")
+    T0 = z["q0"].shape[1]
+    cos, sin = z["cos"][None], z["sin"][None]
+    torch.testing.assert_close(O.rope(z["q0"], cos[:, :T0], sin[:, :T0]), z["q0_rot"], rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(O.rope(z["q1"], cos[:, T0:], sin[:, T0:]), z["q1_rot"], rtol=1e-6, atol=1e-6)
+    B, _, Hk, D = z["k0"].shape
+    kc, vc = torch.zeros(B, 64, Hk, D), torch.zeros(B, 64, Hk, D)
+    keys, _ = O.kv_append(kc, vc, 0, O.rope(z["k0"], cos[:, :T0], sin[:, :T0]), z["v0"])
+    torch.testing.assert_close(keys, z["keys_after_prefill"], rtol=1e-6, atol=1e-6)
+    keys, values = O.kv_append(kc, vc, T0, O.rope(z["k1"], cos[:, T0:], sin[:, T0:]), z["v1"])
+    torch.testing.assert_close(keys, z["keys_after_step"], rtol=1e-6, atol=1e-6)
+    assert torch.equal(values, z["values_after_step"])
+    with pytest.raises(ValueError):
+        O.kv_append(kc, vc, 60, z["k1"], z["v1"])
