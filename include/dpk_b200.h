@@ -61,7 +61,7 @@ const char* dpk_last_error(void);
  * filled / drained, 103/104 the same for an accumulator in tensor memory, 105 a routing
  * index outside the token range, 106 misaligned shared memory; kernel 1 gemm_mn, 2 gemm_mn
  * on CTA pairs, 3 gemm_k, 4 gemm_k on CTA pairs, 5 prefill attention, 6 decode attention,
- * 7 routing, 9 router + norm.  The first report wins until it is read.
+ * 7 routing, 9 router + norm, 11 small-M FFN.  The first report wins until it is read.
  * The reference's device code has no counterpart: its waits are unbounded
  * (DynamicPruningKernels/include/attention_prefill/v3/sm12x_causal.cuh:401,535).
  */
@@ -255,6 +255,21 @@ size_t dpk_attn_decode_workspace_bytes(int B, int Tk, int Hq, int Hk, int D, int
 int dpk_attn_decode(const void* Q, const void* K, const void* V, const uint8_t* mask,
                     const uint32_t* leftpad, void* O, int B, int Tk, int Hq, int Hk, int D, int NG,
                     float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * The same FFN for at most 128 tokens (decode steps), as two launches without any routing
+ * layout: the weights are the M operand of the MMAs, all tokens the N operand, and the routing
+ * mask is applied to the SwiGLU result (routed-out blocks are exact zeros, as in dpk_ffn_swiglu).
+ * Same reference composition as dpk_ffn_swiglu.  mask [M,NG] bytes; H and I multiples of 128
+ * (DPK_ERR_UNSUPPORTED otherwise: use dpk_ffn_swiglu).
+ * Workspace: dpk_ffn_small_workspace_bytes(M,H,I) bytes, 256-byte aligned, ZERO-FILLED ONCE by
+ * the caller before the first call; every call leaves it zero-filled again where it matters, so
+ * it can be reused call after call (by one stream at a time) without a memset.
+ */
+size_t dpk_ffn_small_workspace_bytes(int64_t M, int H, int I);
+int dpk_ffn_swiglu_small(const void* x, const void* Wg, const void* Wu, const void* Wd,
+                         const uint8_t* mask, void* y, int64_t M, int H, int I, int NG, int dtype,
+                         void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Token router fused with the RMSNorm that reads the same hidden state (reference:

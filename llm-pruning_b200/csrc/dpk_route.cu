@@ -159,6 +159,79 @@ route_scatter_kernel(const uint8_t* __restrict__ mask, int64_t M, int NG, int nr
     }
 }
 
+// All three passes in one launch when the tokens fit one row block (M <= 256: decode batches):
+// the only row block's offsets are zero, so no scan is needed -- count, write counts and the
+// packed bits, then write the layout from the same shared-memory tile.
+__global__ void __launch_bounds__(kRouteThreads)
+route_one_block_kernel(const uint8_t* __restrict__ mask, int64_t M, int NG,
+                       int32_t* __restrict__ counts, uint8_t* __restrict__ sorted_mask,
+                       int64_t* __restrict__ sorted_indices, uint32_t* __restrict__ row_bits,
+                       uint32_t* __restrict__ win_bits, int words)
+{
+    __shared__ uint8_t tile[kRouteRows][kRouteCols + 4];
+    __shared__ uint32_t win_or[kRouteThreads / 32];
+    __shared__ int32_t col_cnt[kRouteCols];
+    const int b = blockIdx.z;
+    const int c0 = blockIdx.y * kRouteCols;
+    const int64_t boff = static_cast<int64_t>(b) * M * NG;
+    mask += boff;
+    sorted_mask += boff;
+    sorted_indices += boff;
+    counts += static_cast<int64_t>(b) * NG;
+    route_load_tile(mask, M, NG, 0, c0, tile);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int col = warp; col < kRouteCols; col += kRouteThreads / 32) {
+        int total = 0;
+        for (int chunk = 0; chunk < kRouteRows / 32; ++chunk)
+            total += __popc(__ballot_sync(0xffffffffu, tile[chunk * 32 + lane][col] != 0));
+        if (lane == 0) {
+            col_cnt[col] = total;
+            if (c0 + col < NG) counts[c0 + col] = total;
+        }
+    }
+    if (row_bits != nullptr) {
+        uint32_t acc = 0;
+        for (int i = 0; i < 32; ++i) {
+            const int row = warp * 32 + i;
+            const uint32_t bits = __ballot_sync(0xffffffffu, tile[row][lane] != 0);
+            acc |= bits;
+            if (lane == 0 && row < M) row_bits[static_cast<int64_t>(row) * words + blockIdx.y] = bits;
+        }
+        if (lane == 0) win_or[warp] = acc;
+    }
+    __syncthreads();
+    if (row_bits != nullptr && threadIdx.x < 2 && threadIdx.x * 128 < M) {
+        const int w0 = threadIdx.x * 4;
+        win_bits[static_cast<int64_t>(threadIdx.x) * words + blockIdx.y] =
+            win_or[w0] | win_or[w0 + 1] | win_or[w0 + 2] | win_or[w0 + 3];
+    }
+    for (int i = threadIdx.x; i < kRouteRows * kRouteCols; i += kRouteThreads) {
+        const int row = i / kRouteCols, col = i % kRouteCols;
+        if (row < M && c0 + col < NG)
+            sorted_mask[static_cast<int64_t>(row) * NG + c0 + col] = row < col_cnt[col] ? 1 : 0;
+    }
+    const unsigned lt = (1u << lane) - 1u;
+    for (int col = warp; col < kRouteCols; col += kRouteThreads / 32) {
+        const int c = c0 + col;
+        if (c >= NG) break;
+        int act_base = 0, ina_base = col_cnt[col];
+        for (int chunk = 0; chunk < kRouteRows / 32; ++chunk) {
+            const int r = chunk * 32 + lane;
+            const bool valid = r < M;
+            const bool on = tile[r][col] != 0;
+            const unsigned bal = __ballot_sync(0xffffffffu, on);
+            const unsigned off = __ballot_sync(0xffffffffu, valid) & ~bal;
+            if (valid) {
+                const int pos = on ? act_base + __popc(bal & lt) : ina_base + __popc(off & lt);
+                sorted_indices[static_cast<int64_t>(pos) * NG + c] = r;
+            }
+            act_base += __popc(bal);
+            ina_base += __popc(off);
+        }
+    }
+}
+
 // counts of a caller-supplied sorted_mask.  The layout puts every active row of a column
 // before every inactive one (the invariant the reference's kernels rely on as well,
 // include/gemm_mn/v1/sm12x.cuh:272-311), so the count is the position of the first zero:
@@ -372,6 +445,12 @@ int dpk_route_compact(const uint8_t* mask, int batches, int64_t M, int NG, uint8
     DPK_REQUIRE(ncb <= 65535, "NG=%d too large", NG);
     int32_t* block_cnt = static_cast<int32_t*>(workspace);
     dim3 grid(nrb, ncb, batches);
+    if (nrb == 1) {
+        route_one_block_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, counts, sorted_mask,
+                                                               sorted_indices, nullptr, nullptr, 0);
+        DPK_CUDA(cudaGetLastError());
+        return DPK_OK;
+    }
     route_count_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt, nullptr, nullptr, 0);
     int total = batches * NG;
     route_scan_kernel<<<(total + 127) / 128, 128, 0, s>>>(block_cnt, nrb, NG, batches, counts);
@@ -463,6 +542,12 @@ int dpk_route_plan(const uint8_t* mask, int64_t M, int NG, uint8_t* sorted_mask,
     int ncb = (NG + kRouteCols - 1) / kRouteCols;     // == words of the packed bits
     int32_t* block_cnt = static_cast<int32_t*>(workspace);
     dim3 grid(nrb, ncb, 1);
+    if (nrb == 1) {
+        route_one_block_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, counts, sorted_mask,
+                                                               sorted_indices, row_bits, win_bits, ncb);
+        DPK_CUDA(cudaGetLastError());
+        return DPK_OK;
+    }
     route_count_kernel<<<grid, kRouteThreads, 0, s>>>(mask, M, NG, nrb, block_cnt, row_bits, win_bits,
                                                        ncb);
     route_scan_kernel<<<(NG + 127) / 128, 128, 0, s>>>(block_cnt, nrb, NG, 1, counts);

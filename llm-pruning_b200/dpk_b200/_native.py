@@ -47,6 +47,9 @@ SIGNATURES = {
     "dpk_attn_decode_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32, _i32, _i32]),
     "dpk_attn_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32,
                                _f32, _i32, _vp, _sz, _vp]),
+    "dpk_ffn_small_workspace_bytes": (_sz, [_i64, _i32, _i32]),
+    "dpk_ffn_swiglu_small": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp,
+                                    _sz, _vp]),
     "dpk_router_norm": (_i32, [_vp, _i64, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64,
                                _i32, _i32, _i32, _i32, _i32, _vp]),
     "dpk_rope_append": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _i32,

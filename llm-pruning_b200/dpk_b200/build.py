@@ -38,6 +38,7 @@ SOURCES = [
     "dpk_peer.cu",
     "dpk_router_norm.cu",
     "dpk_rope.cu",
+    "dpk_ffn_small.cu",
 ]
 
 NVCC_FLAGS = [

@@ -54,6 +54,13 @@ class RoutedFFN:
         self.acc_bytes = self.lib.dpk_gemm_k_workspace_bytes(M, H)
         self.acc = torch.empty(max(self.acc_bytes, 16), dtype=u8, device=dev)
         self.launches_per_call = 3 + 1 + 1       # routing plan (3 kernels), gate/up, down
+        # decode-sized calls (at most 128 tokens): two launches, no routing layout; the workspace
+        # is zero-filled here once and left zero by every call
+        self.small_tokens = 128 if (H % 128 == 0 and I % 128 == 0) else 0
+        self.small_ws = None
+        if self.small_tokens:
+            n = self.lib.dpk_ffn_small_workspace_bytes(min(max_tokens, 128), H, I)
+            self.small_ws = torch.zeros(n, dtype=u8, device=dev)
         # tensor-parallel ranks: a dpk_b200.peer.RowParallelSum of width H makes the down
         # projection store its partial sums into the owners' memory and return the summed y
         self.row_parallel = None
@@ -87,6 +94,21 @@ class RoutedFFN:
             (M, self.H), dtype=xf.dtype, device=self.device)
         lib, st, ck = self.lib, _stream(), N.check
         H, I, NG = self.H, self.I, self.NG
+        if 0 < M <= self.small_tokens and self.row_parallel is None and residual is None:
+            ev = None
+            if events is not None:
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+                ev[0].record()
+            ck(lib.dpk_ffn_swiglu_small(xf.data_ptr(), self.wg.data_ptr(), self.wu.data_ptr(),
+                                        self.wd.data_ptr(), m8.data_ptr(), y.data_ptr(), M, H, I, NG,
+                                        self.code, self.small_ws.data_ptr(), self.small_ws.numel(), st))
+            if ev is not None:
+                ev[1].record()
+                events.setdefault("gemm_mn", []).append((ev[0], ev[1]))     # both launches
+                events.setdefault("gemm_k", []).append((ev[1], ev[1]))
+            if chunk_done is not None:
+                chunk_done(y)
+            return y.reshape(*lead, self.H)
         ck(lib.dpk_route_plan(m8.data_ptr(), M, NG, self.sorted_mask.data_ptr(),
                               self.sorted_indices.data_ptr(), self.counts.data_ptr(),
                               self.row_bits.data_ptr(), self.win_bits.data_ptr(),

@@ -377,6 +377,15 @@ def ffn_swiglu(x: torch.Tensor, gate_weight: torch.Tensor, up_weight: torch.Tens
     m8 = _mask_bytes(Mask.flatten(0, 1))
     y = out.view(M, H) if out is not None else torch.empty((M, H), dtype=x.dtype, device=dev)
     lib = N.load()
+    if 0 < M <= 128 and H % 128 == 0 and I % 128 == 0 and I % NG == 0:
+        # decode-sized call: two launches, no routing layout; the workspace has to start zero
+        nbytes = lib.dpk_ffn_small_workspace_bytes(M, H, I)
+        with torch.cuda.device(dev):
+            ws = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+            N.check(lib.dpk_ffn_swiglu_small(xf.data_ptr(), wg.data_ptr(), wu.data_ptr(),
+                                             wd.data_ptr(), m8.data_ptr(), y.data_ptr(), M, H, I, NG,
+                                             code, ws.data_ptr(), nbytes, _stream()))
+        return y.reshape(Bsz, T, H)
     nbytes = lib.dpk_ffn_workspace_bytes(M, H, I, NG)
     ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):

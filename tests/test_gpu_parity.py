@@ -884,3 +884,42 @@ def test_rope_in_place_without_cache_d128_fp16(ops):
     for got, x in ((q2, q), (k2, k)):
         want = O.rope(x, cos[None], sin[None])
         assert ((got.float().cpu() - want).abs() <= want.abs() * 2 ** -11 + 1e-4).all()
+
+
+@pytest.mark.parametrize("M,H,I,NG,keep", [(64, 4096, 14336, 112, 56),     # config 4 decode step
+                                           (1, 256, 512, 4, 2),
+                                           (17, 512, 1024, 16, 5),        # 64-channel groups
+                                           (128, 384, 640, 5, 3),         # full 128 tokens, odd tiles
+                                           (100, 1024, 2048, 2, 1)])      # groups wider than a tile
+def test_ffn_small_m_two_launch_path(ops, M, H, I, NG, keep):
+    """At most 128 tokens: weights as the M operand, mask applied to the SwiGLU result, split
+    reduction with the last CTA converting.  Called three times in a row on one RoutedFFN: the
+    workspace must come back zero-filled, so the results have to be identical."""
+    from dpk_b200.ffn import RoutedFFN
+
+    bf = torch.bfloat16
+    g = seeded(M * 7 + NG)
+    x = bf16r(torch.randn(1, M, H, generator=g))
+    wg = bf16r(torch.randn(I, H, generator=g) * H ** -0.5)
+    wu = bf16r(torch.randn(I, H, generator=g) * H ** -0.5)
+    wd = bf16r(torch.randn(H, I, generator=g) * I ** -0.5)
+    mask = O.topk_route_mask(torch.randn(1, M, NG, generator=g), keep)
+    if M > 2:
+        mask[0, 1] = False                       # a token that uses no group: its row is zero
+    ffn = RoutedFFN(dev(wg, bf), dev(wu, bf), dev(wd, bf), NG, 256)
+    assert ffn.small_tokens == 128
+    outs = [ffn(dev(x, bf), dev(mask)).clone() for _ in range(3)]
+    # fp32 partial sums are added in arrival order: repeated calls agree to a bf16 rounding
+    # (one bf16 ulp of the largest entries is more than 1e-2 of the RMS)
+    for o in outs[1:]:
+        assert_rel(o, outs[0].float().cpu(), tol=3e-2)
+    zero_part = ((max(H, I) // 128 * 4 + 255) // 256 * 256) + 128 * max(2 * I, H) * 4   # counters + accumulator
+    assert int(ffn.small_ws[:zero_part].view(torch.int32).abs().max()) == 0
+    rows = torch.arange(M) if M <= 64 else torch.randperm(M, generator=g)[:48]
+    want = O.ffn_swiglu(x[:, rows], wg, wu, wd, mask[:, rows], round_intermediate=bf)
+    assert_rel(outs[0][:, dev(rows)], want)
+    if M > 2:
+        assert float(outs[0][0, 1].abs().max()) == 0.0
+    # the operator-level entry takes the same path
+    y2 = ops.ffn_swiglu(dev(x, bf), dev(wg, bf), dev(wu, bf), dev(wd, bf), dev(mask))
+    assert_rel(y2, outs[0].float().cpu(), tol=3e-2)
