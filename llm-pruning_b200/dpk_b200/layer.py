@@ -63,6 +63,65 @@ class RoutedDecoderLayer:
         self.sum_o = RowParallelSum.connect(max_tokens, self.H, dt, dev, self.pg)
         self.ffn.row_parallel = RowParallelSum.connect(max_tokens, self.H, dt, dev, self.pg)
 
+    def set_front_end(self, attn_router, ffn_router, input_norm_weight: torch.Tensor,
+                      post_norm_weight: torch.Tensor, eps: float, attn_range=None, ffn_range=None) -> None:
+        """Give the layer its own routers and norms, so that :meth:`forward_full` runs what
+        ``WrapperDecoderLayer.forward`` runs (``WIDE/wrapper/attn_group_ffn_block.py:148-218``).
+        ``attn_router`` / ``ffn_router``: ``(w_down [R,H], b_down, w_route [2*NG,R], b_route)`` of
+        the replicated routers over ALL groups; ``attn_range`` / ``ffn_range``: the ``(g0, g1)``
+        group columns this rank owns (``None`` = all)."""
+        self.front = dict(attn=attn_router, ffn=ffn_router, n1=input_norm_weight.contiguous(),
+                          n2=post_norm_weight.contiguous(), eps=eps, ar=attn_range, fr=ffn_range)
+
+    def forward_full(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                     return_masks: bool = False):
+        """The whole pruned layer from the residual stream ``x [B,T,H]``:
+
+        ``execute_attn = decide(router_attention(x))``, ``h = input_layernorm(x)`` (one kernel);
+        routed Q projection and dense K/V projections of ``h``; rotary embedding; routed
+        attention; routed output projection, summed over the ranks, ``x1 = x + o``;
+        ``execute_ffn = decide(router_ffn(x1))``, ``h2 = post_attention_layernorm(x1)`` (one
+        kernel); routed FFN of ``h2``, summed over the ranks; ``x1 + y``.
+        ``return_masks``: also return this rank's two routing masks."""
+        f = self.front
+        B, T, H = x.shape
+        self._mark("start")
+        am, h, _ = ops.router_norm(x, *f["attn"], norm_weight=f["n1"], eps=f["eps"])
+        if f["ar"] is not None:
+            am = am[..., f["ar"][0]:f["ar"][1]]
+        self._mark("route1")
+        q, meta = ops.gemm_mn(h, self.wq, am)
+        k = (h @ self.wk.T).view(B, T, self.Hk, self.D)
+        v = (h @ self.wv.T).view(B, T, self.Hk, self.D)
+        q = q.view(B, T, self.Hq, self.D)
+        ops.rope_append(q, k, None, cos, sin)
+        self._mark("qkv")
+        meta_attn = meta if B == 1 else {}
+        attn, _ = ops.attention_prefill(q, k, v, am, **meta_attn)
+        self._mark("attn")
+        if self.sum_o is not None:
+            x1 = self.sum_o.routed_gemm_k(attn.view(B, T, self.Hq * self.D), self.wo, am,
+                                          residual=x.contiguous())
+        else:
+            o, _ = ops.gemm_k(attn.view(B, T, self.Hq * self.D), self.wo, am, **meta)
+            if self.world > 1:
+                dist.all_reduce(o, group=self.pg)
+            x1 = x + o
+        self._mark("oproj")
+        fm, h2, _ = ops.router_norm(x1, *f["ffn"], norm_weight=f["n2"], eps=f["eps"])
+        if f["fr"] is not None:
+            fm = fm[..., f["fr"][0]:f["fr"][1]]
+        self._mark("route2")
+        if self.ffn.row_parallel is not None:
+            out = self.ffn(h2, fm, residual=x1)
+        else:
+            y = self.ffn(h2, fm)
+            if self.world > 1:
+                dist.all_reduce(y, group=self.pg)
+            out = x1 + y
+        self._mark("ffn")
+        return (out, am, fm) if return_masks else out
+
     def _mark(self, name):
         if self.timers is not None:
             ev = torch.cuda.Event(enable_timing=True)

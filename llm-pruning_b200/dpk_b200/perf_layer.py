@@ -48,6 +48,10 @@ def main(argv=None):
     ap.add_argument("--sm-margin", type=int, default=-1, help="-1 = automatic: 8 when chunked")
     ap.add_argument("--sweep", default="", help='e.g. "1:0,2:8,4:8,4:16"')
     ap.add_argument("--skip-dense", action="store_true")
+    ap.add_argument("--full", action="store_true",
+                    help="include what surrounds the operators in the reference's layer: the two "
+                         "token routers with their decisions, both RMSNorms and the rotary embedding "
+                         "(the routing then comes from the routers, not from a top-k of given logits)")
     ap.add_argument("--nccl-sums", action="store_true",
                     help="N > 1: sum the partial outputs with NCCL all-reduces instead of the "
                          "fused row-parallel sums")
@@ -84,7 +88,26 @@ def main(argv=None):
     la = torch.randn(1, T, NGA, generator=gx, device=dev)
     lf = torch.randn(1, T, NGF, generator=gx, device=dev)
 
+    if args.full:
+        R = 16
+        def router(ng, keep_frac):
+            wdn = (torch.randn(R, H, generator=gx, device=dev) / H ** 0.5).to(bf)
+            wrt = (torch.randn(2 * ng, R, generator=gx, device=dev) / R ** 0.5).to(bf)
+            brt = torch.zeros(2 * ng, device=dev)
+            # logits of a pair differ by N(0, 2): shift the "execute" logit to the wanted quantile
+            brt[0::2] = 2 ** 0.5 * torch.distributions.Normal(0.0, 1.0).icdf(torch.tensor(keep_frac)).item()
+            return wdn, torch.zeros(R, device=dev).to(bf), wrt, brt.to(bf)
+        n1 = (1.0 + 0.1 * torch.randn(H, generator=gx, device=dev)).to(bf)
+        n2 = (1.0 + 0.1 * torch.randn(H, generator=gx, device=dev)).to(bf)
+        layer.set_front_end(router(NGA, KEEPA / NGA), router(NGF, KEEPF / NGF), n1, n2, 1e-5,
+                            (ga0, ga1), (gf0, gf1))
+        inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device=dev).float() / D))
+        ang = torch.arange(T, device=dev).float()[:, None] * inv[None, :]
+        cos, sin = torch.cat([ang, ang], -1).cos().to(bf), torch.cat([ang, ang], -1).sin().to(bf)
+
     def step():
+        if args.full:
+            return layer.forward_full(x, cos, sin)
         am = ops.topk_route_mask(la, KEEPA)[..., ga0:ga1]
         fm = ops.topk_route_mask(lf, KEEPF)[..., gf0:gf1]
         return layer(x, am, fm)
@@ -149,7 +172,8 @@ def main(argv=None):
     for _ in range(3):
         step()
     torch.cuda.synchronize()
-    names = ["start", "qkv", "attn", "oproj", "ar1", "ffn", "ar2"]
+    names = (["start", "route1", "qkv", "attn", "oproj", "route2", "ffn"] if args.full else
+             ["start", "qkv", "attn", "oproj", "ar1", "ffn", "ar2"])
     phases = {}
     tm = layer.timers
     for a, b in zip(names[:-1], names[1:]):
@@ -166,8 +190,27 @@ def main(argv=None):
         wg, wu, wd = layer.ffn.wg, layer.ffn.wu, layer.ffn.wd
         sdpa = torch.nn.functional.scaled_dot_product_attention
 
+        def rot(t):
+            half = D // 2
+            return t * cos[None, :, None, :] + torch.cat((-t[..., half:], t[..., :half]), -1) * sin[None, :, None, :]
+
         def dense_step():
             xf = x[0]
+            if args.full:
+                xn = torch.nn.functional.rms_norm(xf, (H,), n1, 1e-5)
+                q = rot((xn @ wq.T).view(1, T, hq_l, D)).transpose(1, 2)
+                k = rot((xn @ wk.T).view(1, T, hk_l, D)).transpose(1, 2)
+                v = (xn @ wv.T).view(1, T, hk_l, D).transpose(1, 2)
+                a = sdpa(q, k, v, is_causal=True, enable_gqa=True).transpose(1, 2).reshape(T, hq_l * D)
+                o = a @ wo.T
+                if world > 1:
+                    dist.all_reduce(o)
+                x1 = xf + o
+                x1n = torch.nn.functional.rms_norm(x1, (H,), n2, 1e-5)
+                yy = (torch.nn.functional.silu(x1n @ wg.T) * (x1n @ wu.T)) @ wd.T
+                if world > 1:
+                    dist.all_reduce(yy)
+                return x1 + yy
             q = (xf @ wq.T).view(1, T, hq_l, D).transpose(1, 2)
             k = (xf @ wk.T).view(1, T, hk_l, D).transpose(1, 2)
             v = (xf @ wv.T).view(1, T, hk_l, D).transpose(1, 2)
@@ -212,6 +255,7 @@ def main(argv=None):
             "roofline": {"bound": "tensor", "achieved": ach, "peak": peak_tf * world,
                          "unit": "TFLOP/s", "frac": ach / (peak_tf * world),
                          "peak_source": src + f" sustained bf16 x {world} GPUs"},
+            "full_layer": bool(args.full),
             "data": "synthetic, seed %d" % SEED}))
     if world > 1:
         dist.destroy_process_group()

@@ -923,3 +923,51 @@ def test_ffn_small_m_two_launch_path(ops, M, H, I, NG, keep):
     # the operator-level entry takes the same path
     y2 = ops.ffn_swiglu(dev(x, bf), dev(wg, bf), dev(wu, bf), dev(wd, bf), dev(mask))
     assert_rel(y2, outs[0].float().cpu(), tol=3e-2)
+
+
+def test_routed_decoder_layer_full_front_end(ops):
+    """The whole layer from the residual stream: routers + decisions + norms (one kernel each),
+    projections, rotary embedding, routed attention, routed FFN -- against the oracle composition
+    run with the masks the layer decided, and the decisions themselves against the oracle router
+    wherever its pair of logits is clearly apart."""
+    from dpk_b200.layer import RoutedDecoderLayer
+
+    bf = torch.bfloat16
+    g = seeded(41)
+    T, H, Hq, Hk, D, I, NGF, R = 300, 256, 8, 2, 64, 1024, 8, 16
+    ws = {n: bf16r(torch.randn(*shp, generator=g) * 0.05) for n, shp in dict(
+        wq=(Hq * D, H), wk=(Hk * D, H), wv=(Hk * D, H), wo=(H, Hq * D),
+        wg=(I, H), wu=(I, H), wd=(H, I)).items()}
+    def router(ng):
+        return (bf16r(torch.randn(R, H, generator=g) * H ** -0.5), bf16r(torch.randn(R, generator=g) * 0.1),
+                bf16r(torch.randn(2 * ng, R, generator=g) * R ** -0.5), bf16r(torch.randn(2 * ng, generator=g) * 0.1))
+    ra, rf = router(Hk), router(NGF)
+    n1 = bf16r(1.0 + 0.1 * torch.randn(H, generator=g))
+    n2 = bf16r(1.0 + 0.1 * torch.randn(H, generator=g))
+    x = bf16r(torch.randn(1, T, H, generator=g))
+    ang = torch.arange(T).float()[:, None] / (10000.0 ** (torch.arange(0, D, 2).float() / D))[None, :]
+    cos, sin = bf16r(torch.cat([ang, ang], -1).cos()), bf16r(torch.cat([ang, ang], -1).sin())
+    layer = RoutedDecoderLayer(*(dev(ws[n], bf) for n in ("wq", "wk", "wv", "wo", "wg", "wu", "wd")),
+                               num_q_heads=Hq, num_kv_heads=Hk, head_dim=D, attn_groups=Hk,
+                               ffn_groups=NGF, max_tokens=T)
+    layer.set_front_end(tuple(dev(t, bf) for t in ra), tuple(dev(t, bf) for t in rf), dev(n1, bf),
+                        dev(n2, bf), 1e-5)
+    out, am, fm = layer.forward_full(dev(x, bf), dev(cos, bf), dev(sin, bf), return_masks=True)
+    am, fm = am.cpu(), fm.cpu()
+    # decisions of the first router
+    la, ea = O.bottleneck_router(x, *ra, module_dtype=bf)
+    clear = (la[..., 0] - la[..., 1]).abs() > 6e-2
+    assert torch.equal(am[clear], ea[clear]) and clear.float().mean() > 0.8
+    # oracle composition with the layer's masks and the same bf16 hand-offs
+    h = O.rms_norm(x.to(bf), n1, 1e-5).float()
+    q = bf16r(O.rope(bf16r(O.gemm_mn(h, ws["wq"], am)).view(1, T, Hq, D), cos[None], sin[None]))
+    k = bf16r(O.rope(bf16r(h @ ws["wk"].T).view(1, T, Hk, D), cos[None], sin[None]))
+    v = bf16r(h @ ws["wv"].T).view(1, T, Hk, D)
+    a = bf16r(O.attention_prefill(q, k, v, am)).view(1, T, Hq * D)
+    x1 = bf16r(x + bf16r(O.gemm_k(a, ws["wo"], am)))
+    lf, ef = O.bottleneck_router(x1, *rf, module_dtype=bf)
+    clear = (lf[..., 0] - lf[..., 1]).abs() > 1e-1          # x1 itself carries bf16 differences
+    assert torch.equal(fm[clear], ef[clear]) and clear.float().mean() > 0.7
+    h2 = O.rms_norm(x1.to(bf), n2, 1e-5).float()
+    want = x1 + O.ffn_swiglu(h2, ws["wg"], ws["wu"], ws["wd"], fm, round_intermediate=bf)
+    assert_rel(out, want, tol=3e-2)
