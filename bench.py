@@ -221,6 +221,9 @@ def main():
                     help="N > 1: how the ranks' partial outputs are added: 'fused' = the down "
                          "projection stores its partial windows into the owning rank's memory and a "
                          "reduce+gather kernel finishes the sum; 'nccl' = NCCL all-reduce")
+    ap.add_argument("--halves", type=int, default=2, choices=[1, 2],
+                    help="--sum fused: 2 = project the tokens in two halves and gather the first half "
+                         "under the second half's projection")
     ap.add_argument("--ar-chunks", type=int, default=0,
                     help="N > 1: token chunks of the down projection whose all-reduces overlap "
                          "the next chunk's compute (0 = automatic: 4 chunks on 2 GPUs, where the "
@@ -273,6 +276,7 @@ def main():
     if fused:
         from dpk_b200.peer import RowParallelSum
         ffn.row_parallel = RowParallelSum.connect(M_TOK, HID, torch.bfloat16, device)
+        ffn.row_parallel.halves = args.halves
         args.ar_chunks, args.sm_margin = 1, 0
     if args.ar_chunks <= 0:
         args.ar_chunks = 4 if world == 2 else 1
@@ -297,7 +301,7 @@ def main():
             wk.wait()
         return y_out
 
-    launches_per_step = 1 + ffn.launches_per_call + (1 if fused else chunks - 1)
+    launches_per_step = 1 + ffn.launches_per_call + ((2 * args.halves - 1) if fused else chunks - 1)
 
     # ---- device-resident timing -----------------------------------------------------
     for _ in range(args.warmup):
@@ -441,8 +445,9 @@ def main():
                    "parallelism": "single GPU" if world == 1 else
                    (f"tp{world} by channel groups ({gpr} groups per rank); the down projection stores "
                     "its partial token windows into the owning rank's memory (NVLink), a reduce+gather "
-                    "kernel adds them and hands the rows to every rank; two one-element all-reduces as "
-                    "barriers" if fused else
+                    "kernel adds them and hands the rows to every rank; one-element all-reduces as "
+                    f"barriers; tokens in {args.halves} part(s), the first part's gather under the second "
+                    "part's projection" if fused else
                     f"tp{world} by channel groups ({gpr} groups per rank) + NCCL all-reduce of y in "
                     f"{chunks} token chunks overlapping the down projection, {args.sm_margin} SMs "
                     "left to the collective"),

@@ -343,10 +343,12 @@ int dpk_gemm_k_scatter(const void* A, int64_t lda, const void* W, int64_t ldw,
                        void* stream);
 
 /* stage: this rank's own staging buffer; out: host array of `world` device pointers;
- * residual: optional local [M,ld] added to the sum (NULL for none). */
+ * residual: optional local [M,ld] added to the sum (NULL for none); max_blocks: upper bound
+ * of the grid (0 = fill the GPU) -- a caller that runs this kernel beside a projection on
+ * another stream passes about one block per SM so that both fit. */
 int dpk_reduce_gather(const void* stage, void* const* out, const void* residual, int world,
                       int rank, int64_t rows_per_owner, int64_t M, int N, int64_t ld, int dtype,
-                      void* stream);
+                      int max_blocks, void* stream);
 
 #ifdef __cplusplus
 }

@@ -125,7 +125,7 @@ extern "C" int dpk_peer_free(void* ptr)
 
 extern "C" int dpk_reduce_gather(const void* stage, void* const* out, const void* residual, int world,
                                  int rank, int64_t rows_per_owner, int64_t M, int N, int64_t ld,
-                                 int dtype, void* stream)
+                                 int dtype, int max_blocks, void* stream)
 {
     DPK_REQUIRE(stage && out, "NULL tensor");
     DPK_REQUIRE(dtype == DPK_F16 || dtype == DPK_BF16, "dtype must be DPK_F16 or DPK_BF16");
@@ -152,13 +152,15 @@ extern "C" int dpk_reduce_gather(const void* stage, void* const* out, const void
     if (p.rows == 0) return DPK_OK;
     const int64_t total = p.rows * (N / 8);
     int64_t blocks = (total + 255) / 256;
-    const int64_t cap = int64_t(sm_count()) * 8;
+    const int64_t cap = max_blocks > 0 ? max_blocks : int64_t(sm_count()) * 8;
     if (blocks > cap) blocks = cap;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // capped grid: small blocks, so that one of them fits on an SM beside a projection CTA
+    const int threads = max_blocks > 0 ? 128 : 256;
     if (dtype == DPK_BF16)
-        reduce_gather_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, s>>>(p);
+        reduce_gather_kernel<true><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
     else
-        reduce_gather_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, s>>>(p);
+        reduce_gather_kernel<false><<<static_cast<unsigned>(blocks), threads, 0, s>>>(p);
     DPK_CUDA(cudaGetLastError());
     return DPK_OK;
 }

@@ -62,7 +62,7 @@ SIGNATURES = {
     "dpk_gemm_k_scatter": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, C.POINTER(_vp), _i32, _i32, _i64,
                                   _i64, _i64, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "dpk_reduce_gather": (_i32, [_vp, C.POINTER(_vp), _vp, _i32, _i32, _i64, _i64, _i32, _i64, _i32,
-                                 _vp]),
+                                 _i32, _vp]),
 }
 
 _lib = None

@@ -79,8 +79,10 @@ class RowParallelSum:
         self.world, self.rank, self.max_rows, self.width = world, rank, max_rows, width
         self.dtype, self.device = dtype, device
         self.stage, self.out = stage, out
-        self._stage_tab, self._out_tab = _ptr_table(stage_ptrs), _ptr_table(out_ptrs)
+        self._stage_ptrs, self._out_ptrs = list(stage_ptrs), list(out_ptrs)
         self._barrier = barrier
+        self.halves = 1          # 2: split the tokens; the second half's projection hides the first half's gather
+        self._side = None
         self._keep = keep
         self.lib = N.load()
         self.code = 1 if dtype == torch.bfloat16 else 0
@@ -90,7 +92,8 @@ class RowParallelSum:
     # ---- construction -----------------------------------------------------------------
     @staticmethod
     def _sizes(world: int, max_rows: int, width: int):
-        R = rows_per_owner(max_rows, world)
+        # two halves round their shares up separately: two more windows per rank cover both
+        R = rows_per_owner(max_rows, world) + 2 * WINDOW
         return R, world * R * width * 2
 
     @classmethod
@@ -137,44 +140,91 @@ class RowParallelSum:
                     raws[r][nbytes:].view(dtype), bases, [b + nbytes for b in bases],
                     lambda: None, keep=tuple(raws)) for r in range(world)]
 
-    # ---- the two halves ---------------------------------------------------------------
+    # ---- the two kernels ------------------------------------------------------------------
+    def _part(self, M: int, part: Optional[int]):
+        """Rows ``[row0, row0+rows)`` of a call and where their staging slabs start (elements)."""
+        if part is None:
+            return 0, M, 0
+        M0 = min(M, ((M + 1) // 2 + WINDOW - 1) // WINDOW * WINDOW)
+        if part == 0:
+            return 0, M0, 0
+        return M0, M - M0, self.world * rows_per_owner(M0, self.world) * self.width
+
     def scatter(self, A2: torch.Tensor, W: torch.Tensor, row_bits: torch.Tensor,
-                win_bits: torch.Tensor, NG: int) -> None:
-        """First half: this rank's partial sums go to the owners' staging buffers."""
+                win_bits: torch.Tensor, NG: int, part: Optional[int] = None) -> None:
+        """Projection kernel: this rank's partial sums go to the owners' staging buffers
+        (``part``: ``None`` = all rows, 0 / 1 = first / second half of the tokens)."""
         M, K = A2.shape
         if M > self.max_rows or W.shape != (self.width, K):
             raise ValueError("shape outside what this RowParallelSum was built for")
-        R = rows_per_owner(M, self.world)
-        need = self.lib.dpk_gemm_k_scatter_workspace_bytes(M, self.width, self.width)
+        row0, rows, soff = self._part(M, part)
+        if rows <= 0:
+            return
+        R = rows_per_owner(rows, self.world)
+        need = self.lib.dpk_gemm_k_scatter_workspace_bytes(rows, self.width, self.width)
         if need and (self._ws is None or self._ws.numel() < need):
             self._ws = torch.empty(need, dtype=torch.uint8, device=self.device)
+        esz = A2.element_size()
+        words = row_bits.shape[1]
+        stage_tab = _ptr_table([b + soff * 2 for b in self._stage_ptrs])
         N.check(self.lib.dpk_gemm_k_scatter(
-            A2.data_ptr(), A2.stride(0), W.data_ptr(), W.stride(0), row_bits.data_ptr(),
-            win_bits.data_ptr(), self._stage_tab, self.world, self.rank, R, self.width, M,
-            self.width, K, NG, self.code, self._ws.data_ptr() if need else None, need, _stream()))
+            A2.data_ptr() + row0 * A2.stride(0) * esz, A2.stride(0), W.data_ptr(), W.stride(0),
+            row_bits.data_ptr() + row0 * words * 4, win_bits.data_ptr() + (row0 // WINDOW) * words * 4,
+            stage_tab, self.world, self.rank, R, self.width, rows, self.width, K, NG, self.code,
+            self._ws.data_ptr() if need else None, need, _stream()))
 
-    def reduce(self, M: int, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Second half: sum the received slabs of the rows this rank owns and store them
-        into every rank's output."""
-        R = rows_per_owner(M, self.world)
+    def reduce(self, M: int, residual: Optional[torch.Tensor] = None, part: Optional[int] = None,
+               max_blocks: int = 0) -> torch.Tensor:
+        """Reduce + gather kernel: sum the received slabs of the rows this rank owns and store
+        them into every rank's output."""
         if residual is not None and (residual.shape != (M, self.width) or not residual.is_contiguous()):
             raise ValueError("residual must be a contiguous [M, width] tensor")
-        N.check(self.lib.dpk_reduce_gather(
-            self.stage.data_ptr(), self._out_tab, residual.data_ptr() if residual is not None else None,
-            self.world, self.rank, R, M, self.width, self.width, self.code, _stream()))
+        row0, rows, soff = self._part(M, part)
+        if rows > 0:
+            R = rows_per_owner(rows, self.world)
+            ooff = row0 * self.width * 2
+            out_tab = _ptr_table([b + ooff for b in self._out_ptrs])
+            N.check(self.lib.dpk_reduce_gather(
+                self.stage.data_ptr() + soff * 2, out_tab,
+                residual.data_ptr() + ooff if residual is not None else None, self.world, self.rank, R,
+                rows, self.width, self.width, self.code, max_blocks, _stream()))
         return self.out[:M * self.width].view(M, self.width)
 
     def gemm_k(self, A2: torch.Tensor, W: torch.Tensor, row_bits: torch.Tensor,
                win_bits: torch.Tensor, NG: int, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        M = A2.shape[0]
+        if self.halves == 2 and M >= 4 * WINDOW * self.world:
+            return self._gemm_k_halves(A2, W, row_bits, win_bits, NG, residual)
         self._mark("start")
         self.scatter(A2, W, row_bits, win_bits, NG)
         self._mark("scatter")
         self._barrier()          # every rank's partial sums have landed
         self._mark("barrier1")
-        y = self.reduce(A2.shape[0], residual)
+        y = self.reduce(M, residual)
         self._mark("reduce")
         self._barrier()          # every owner's rows have landed; staging may be reused
         self._mark("barrier2")
+        return y
+
+    def _gemm_k_halves(self, A2, W, row_bits, win_bits, NG, residual):
+        """The tokens in two halves: while the second half is being projected (tensor cores,
+        stores of partial sums), the first half is reduced and gathered on a second stream
+        (loads from local memory, stores over the links) by a grid small enough to share the
+        SMs with the projection."""
+        M = A2.shape[0]
+        main = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        self.scatter(A2, W, row_bits, win_bits, NG, part=0)
+        self._barrier()
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            self.reduce(M, residual, part=0, max_blocks=148)
+        self.scatter(A2, W, row_bits, win_bits, NG, part=1)
+        self._barrier()
+        y = self.reduce(M, residual, part=1)
+        main.wait_stream(self._side)
+        self._barrier()
         return y
 
     def _mark(self, name: str) -> None:

@@ -52,6 +52,9 @@ def main(argv=None):
                     help="include what surrounds the operators in the reference's layer: the two "
                          "token routers with their decisions, both RMSNorms and the rotary embedding "
                          "(the routing then comes from the routers, not from a top-k of given logits)")
+    ap.add_argument("--halves", type=int, default=2, choices=[1, 2],
+                    help="fused sums: 2 = project the tokens in two halves and gather the first "
+                         "half under the second half's projection")
     ap.add_argument("--nccl-sums", action="store_true",
                     help="N > 1: sum the partial outputs with NCCL all-reduces instead of the "
                          "fused row-parallel sums")
@@ -143,6 +146,7 @@ def main(argv=None):
         layer.token_chunks = 1
         nccl_ms = timed(step)
         layer.fuse_sums(T)
+        layer.sum_o.halves = layer.ffn.row_parallel.halves = args.halves
         settings = [(1, 0)]
     tried = {}
     for chunks, margin in settings:
@@ -241,7 +245,7 @@ def main(argv=None):
             "n_gpus": world, "parallelism": f"tp{split}{' (rank 0 alone, no collective)' if split != world else ''}: {hk_l} KV-head groups and {gf1 - gf0} "
             "channel groups per rank, " + (
                 "row-parallel sums fused into the o and down projections (stores into the owning "
-                "rank's memory, reduce + gather kernel, 2 barriers each)" if fused else
+                f"rank's memory, reduce + gather kernel, tokens in {args.halves} part(s))" if fused else
                 f"2 NCCL all-reduces of [T,H] bf16, {chunks} token chunks pipelined, {margin} SMs "
                 "left to the collective"),
             "ms_per_layer_with_nccl_all_reduce": nccl_ms,

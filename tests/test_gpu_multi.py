@@ -55,11 +55,17 @@ def _worker(rank, world, port, ret):
         for _ in range(3):                                    # buffers are reused call after call
             y = ffn(xd, lmask, residual=xd)
         torch.cuda.synchronize()
+        y_one = y.clone()
+        ffn.row_parallel.halves = 2                           # overlapped schedule, second stream
+        for _ in range(3):
+            y = ffn(xd, lmask, residual=xd)
+        torch.cuda.synchronize()
         want = x.float() + O.ffn_swiglu(x.float(), wg.float(), wu.float(), wd.float(), mask,
                                         round_intermediate=bf)
         ret[rank] = dict(
             vs_nccl=O.rel_err(y.float().cpu(), y_nccl.float().cpu()),
             vs_oracle=O.rel_err(y.float().cpu(), want),
+            halves_equal=bool(torch.equal(y, y_one)),
             status=ops.device_status(),
             digest=float(y.float().sum().item()))
     finally:
@@ -76,6 +82,7 @@ def test_fused_row_parallel_ffn_two_ranks():
     assert sorted(out) == list(range(world))
     for r in range(world):
         assert out[r]["status"] == 0
+        assert out[r]["halves_equal"]          # same slabs summed in the same order: same bits
         assert out[r]["vs_oracle"] <= 2e-2, out[r]
         # one rounding of the sum instead of one per partial and one for the residual
         assert out[r]["vs_nccl"] <= 2e-2, out[r]

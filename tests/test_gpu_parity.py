@@ -971,3 +971,39 @@ def test_routed_decoder_layer_full_front_end(ops):
     h2 = O.rms_norm(x1.to(bf), n2, 1e-5).float()
     want = x1 + O.ffn_swiglu(h2, ws["wg"], ws["wu"], ws["wd"], fm, round_intermediate=bf)
     assert_rel(out, want, tol=3e-2)
+
+
+@pytest.mark.parametrize("world,M,N,Kl,NGl", [(4, 2100, 512, 256, 4), (2, 4096, 256, 512, 4),
+                                              (8, 4500, 256, 128, 2)])
+def test_row_parallel_sum_two_halves_emulated(ops, world, M, N, Kl, NGl):
+    """The overlapped schedule's pieces: each half of the tokens is its own scatter / reduce
+    problem with its own ownership split and staging region; together they must give the sum."""
+    from dpk_b200.peer import RowParallelSum
+
+    bf = torch.bfloat16
+    g = seeded(31 * world + M)
+    ranks = RowParallelSum.emulate(world, M, N, bf, torch.device("cuda"))
+    a = [bf16r(torch.randn(1, M, Kl, generator=g)) for _ in range(world)]
+    w = [bf16r(torch.randn(N, Kl, generator=g) / (Kl * world) ** 0.5) for _ in range(world)]
+    mask = [torch.rand(1, M, NGl, generator=g) > 0.5 for _ in range(world)]
+    res = bf16r(torch.randn(M, N, generator=g))
+    want = sum(O.gemm_k(a[r], w[r], mask[r]) for r in range(world))[0] + res
+    words = (NGl + 31) // 32
+    lib = ranks[0].lib
+    packed = []
+    for r in range(world):
+        m8 = dev(mask[r][0]).to(torch.uint8).contiguous()
+        rb = torch.empty((M, words), dtype=torch.int32, device="cuda")
+        wb = torch.empty(((M + 127) // 128, words), dtype=torch.int32, device="cuda")
+        assert lib.dpk_mask_pack(m8.data_ptr(), M, NGl, rb.data_ptr(), wb.data_ptr(), None) == 0
+        packed.append((dev(a[r][0], bf), dev(w[r], bf), rb, wb))
+    resd = dev(res, bf)
+    for part in (0, 1):
+        for r in range(world):
+            ranks[r].scatter(*packed[r], NGl, part=part)
+        for r in range(world):
+            out = ranks[r].reduce(M, resd, part=part, max_blocks=37 if part == 0 else 0)
+    for r in range(world):
+        got = ranks[r].out[:M * N].view(M, N)
+        assert_rel(got, want, tol=3e-2)
+        assert torch.equal(got, ranks[0].out[:M * N].view(M, N))
