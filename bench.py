@@ -275,9 +275,14 @@ def main():
     fused = world > 1 and args.sum == "fused"
     if fused:
         from dpk_b200.peer import RowParallelSum
-        ffn.row_parallel = RowParallelSum.connect(M_TOK, HID, torch.bfloat16, device)
-        ffn.row_parallel.halves = args.halves
-        args.ar_chunks, args.sm_margin = 1, 0
+        try:
+            ffn.row_parallel = RowParallelSum.connect(M_TOK, HID, torch.bfloat16, device)
+            ffn.row_parallel.halves = args.halves
+            args.ar_chunks, args.sm_margin = 1, 0
+        except RuntimeError as exc:       # the same exception on every rank (see connect)
+            if rank == 0:
+                print(f"bench: {exc}; summing the partial outputs with NCCL instead", file=sys.stderr)
+            fused = False
     if args.ar_chunks <= 0:
         args.ar_chunks = 4 if world == 2 else 1
     chunks = args.ar_chunks if world > 1 else 1

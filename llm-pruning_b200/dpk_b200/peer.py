@@ -104,20 +104,43 @@ class RowParallelSum:
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         _, nbytes = cls._sizes(world, max_rows, width)
         lib = N.load()
+        # Every rank takes part in every exchange below even when something failed locally, so
+        # that a failure on one rank becomes the same exception on all of them instead of a
+        # rank waiting in a collective the others never enter.
+        problem = None
         with torch.cuda.device(device):
             base = C.c_void_p()
             handle = C.create_string_buffer(64)
-            N.check(lib.dpk_peer_alloc(2 * nbytes, C.byref(base), handle))
-            handles: List[bytes] = [b""] * world
-            dist.all_gather_object(handles, handle.raw, group=group)
+            try:
+                N.check(lib.dpk_peer_alloc(2 * nbytes, C.byref(base), handle))
+            except Exception as exc:          # noqa: BLE001 - reported to all ranks below
+                problem = f"rank {rank}: {exc}"
+            handles: List[Optional[bytes]] = [None] * world
+            dist.all_gather_object(handles, None if problem else handle.raw, group=group)
             bases = []
-            for r in range(world):
-                if r == rank:
-                    bases.append(base.value)
-                else:
+            if all(h is not None for h in handles):
+                for r in range(world):
+                    if r == rank:
+                        bases.append(base.value)
+                        continue
                     p = C.c_void_p()
-                    N.check(lib.dpk_peer_open(handles[r], C.byref(p)))
-                    bases.append(p.value)
+                    try:
+                        N.check(lib.dpk_peer_open(handles[r], C.byref(p)))
+                        bases.append(p.value)
+                    except Exception as exc:  # noqa: BLE001
+                        problem = problem or f"rank {rank} mapping rank {r}: {exc}"
+                        break
+            elif problem is None:
+                problem = "a peer could not allocate its buffer"
+            problems: List[Optional[str]] = [None] * world
+            dist.all_gather_object(problems, problem, group=group)
+            if any(problems):
+                for q in bases:
+                    if q != base.value:
+                        lib.dpk_peer_close(q)
+                if base.value:
+                    lib.dpk_peer_free(base)
+                raise RuntimeError("peer buffers unavailable: " + "; ".join(x for x in problems if x))
             raw = torch.as_tensor(_DeviceBytes(base.value, 2 * nbytes), device=device)
         stage = raw[:nbytes].view(dtype)
         out = raw[nbytes:].view(dtype)
@@ -126,8 +149,23 @@ class RowParallelSum:
         def barrier():
             dist.all_reduce(token, group=group)
 
-        return cls(world, rank, max_rows, width, dtype, device, stage, out, bases,
+        self = cls(world, rank, max_rows, width, dtype, device, stage, out, bases,
                    [b + nbytes for b in bases], barrier, keep=(raw, token))
+        self._mapped = [b for r, b in enumerate(bases) if r != rank]
+        self._owned = base.value
+        return self
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's.  Collective in effect: call it on every
+        rank, after the last use, with the stream idle."""
+        torch.cuda.synchronize(self.device)
+        for q in getattr(self, "_mapped", []):
+            self.lib.dpk_peer_close(q)
+        if getattr(self, "_owned", None):
+            self.lib.dpk_peer_free(self._owned)
+        self._mapped, self._owned = [], None
+        self.stage = self.out = None
+        self._keep = ()
 
     @classmethod
     def emulate(cls, world: int, max_rows: int, width: int, dtype: torch.dtype,
