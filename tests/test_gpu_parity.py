@@ -1007,3 +1007,35 @@ def test_row_parallel_sum_two_halves_emulated(ops, world, M, N, Kl, NGl):
         got = ranks[r].out[:M * N].view(M, N)
         assert_rel(got, want, tol=3e-2)
         assert torch.equal(got, ranks[0].out[:M * N].view(M, N))
+
+
+def test_simulator_mlp_kernel_convention(ops):
+    """``RoutedMLPKernel.base_prefill`` with the simulator's keywords: token-wise mask [B,S] (a token
+    keeps or skips the whole layer), grouped mask, a single routed layer, biases."""
+    from dpk_b200.sim import RoutedMLPKernel
+
+    bf = torch.bfloat16
+    g = seeded(61)
+    B, S, H, I = 2, 150, 256, 512
+    x = bf16r(torch.randn(B, S, H, generator=g))
+    w_up = bf16r(torch.randn(I, H, generator=g) * H ** -0.5)
+    w_gate = bf16r(torch.randn(I, H, generator=g) * H ** -0.5)
+    w_down = bf16r(torch.randn(H, I, generator=g) * I ** -0.5)
+    tok = torch.rand(B, S, generator=g) > 0.4
+    out = RoutedMLPKernel.base_prefill(x=dev(x, bf), w_up=dev(w_up, bf), w_gate=dev(w_gate, bf),
+                                       w_down=dev(w_down, bf), route_mask=dev(tok), activation="silu",
+                                       estimated_sparsity=0.4, impl="auto", backend="b200")
+    want = O.ffn_swiglu(x, w_gate, w_up, w_down, tok[..., None], round_intermediate=bf)
+    assert_rel(out, want)
+    assert float(out[~dev(tok)].abs().max()) == 0.0                 # skipped tokens come out as zeros
+    grp = torch.rand(B, S, 4, generator=g) > 0.5
+    out = RoutedMLPKernel.base_decode(x=dev(x, bf), w_up=dev(w_up, bf), w_gate=dev(w_gate, bf),
+                                      w_down=dev(w_down, bf), route_mask=dev(grp), activation="relu")
+    h = bf16r(torch.relu(bf16r(O.gemm_mn(x, w_gate, grp))) * bf16r(O.gemm_mn(x, w_up, grp)))
+    assert_rel(out, O.gemm_k(h, w_down, grp), tol=3e-2)
+    b_up = bf16r(torch.randn(I, generator=g) * 0.1)
+    single = RoutedMLPKernel.base_prefill(x=dev(x, bf), w_up=dev(w_up, bf), b_up=dev(b_up, bf),
+                                          route_mask=dev(grp))
+    on = grp.repeat_interleave(I // 4, dim=-1).float()
+    # the projection is rounded to bf16 before the bias is added and the sum rounded again
+    assert_rel_active(single, (O.gemm_mn(x, w_up, grp) + b_up * on), tol=3e-2)
