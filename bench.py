@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the routed dynamic-width FFN path (BASELINE.json config 2).
+"""Benchmark of the routed dynamic-width FFN path (Llama-3-8B-shaped FFN prefill, 8192 tokens).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
@@ -136,7 +136,7 @@ def make_inputs(device, rank_groups=None):
 
 # ------------------------------------------------------------------ CPU baseline
 
-def cpu_baseline(budget_s: float = 12.0):
+def cpu_baseline(seconds: float = 12.0):
     """Times the reference CPU formulation (dense GEMMs, then mask; the oracle's
     ``dense_then_mask_ffn``) on a bounded token sample of the same layer."""
     from oracle import dpk_oracle as O
@@ -155,7 +155,7 @@ def cpu_baseline(budget_s: float = 12.0):
 
     run(64)                                  # warm the thread pool
     t = run(256)
-    tokens = int(min(8192, max(256, 256 * budget_s / max(t, 1e-3))))
+    tokens = int(min(8192, max(256, 256 * seconds / max(t, 1e-3))))
     tokens = (tokens // 128) * 128
     t = run(tokens)
     return {"value": tokens / t, "unit": UNIT, "cores": torch.get_num_threads(),

@@ -334,8 +334,8 @@ static int decode_splits(int B, int Tk, int Hk)
     int splits = Tk / 1024;
     if (splits > kDecMaxSplits) splits = kDecMaxSplits;
     if (splits < 1) splits = 1;
-    const long long budget = 16ll * sm_count();
-    while (splits > 1 && (long long)B * Hk * splits / 2 > budget) splits /= 2;
+    const long long max_ctas = 16ll * sm_count();
+    while (splits > 1 && (long long)B * Hk * splits / 2 > max_ctas) splits /= 2;
     return splits;
 }
 

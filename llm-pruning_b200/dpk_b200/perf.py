@@ -7,10 +7,10 @@ family on seeded synthetic tensors with CUDA events, next to the dense PyTorch
 equivalent (cuBLAS / SDPA), and prints one JSON line per case with the achieved rate
 and its fraction of the measured roofline.
 
-    python -m dpk_b200.perf --kernel attention_prefill      # BASELINE config 3
-    python -m dpk_b200.perf --kernel attention_decode       # BASELINE config 4 (attention)
-    python -m dpk_b200.perf --kernel ffn_decode             # BASELINE config 4 (FFN, 64 tokens)
-    python -m dpk_b200.perf --kernel gemm_mn | gemm_k | ffn # BASELINE config 2 pieces
+    python -m dpk_b200.perf --kernel attention_prefill      # 8192-token routed prefill attention
+    python -m dpk_b200.perf --kernel attention_decode       # decode step, batch 64, 32768-token KV cache
+    python -m dpk_b200.perf --kernel ffn_decode             # decode-step FFN, 64 tokens
+    python -m dpk_b200.perf --kernel gemm_mn | gemm_k | ffn # Llama-3-8B-shaped FFN prefill and its two GEMMs
 """
 
 from __future__ import annotations
@@ -202,7 +202,7 @@ def run_gemm(args, which):
 
 
 def run_router_norm(args):
-    """Router + RMSNorm in front of the config-5 layer: H=8192, 224 FFN groups, rank 16."""
+    """Router + RMSNorm in front of the 70B-shaped layer: H=8192, 224 FFN groups, rank 16."""
     M, H, NG, R = args.tokens or 16384, args.hidden or 8192, 224, 16
     gen = torch.Generator(device="cuda").manual_seed(SEED)
     bf = torch.bfloat16

@@ -1,4 +1,4 @@
-"""Throughput of the Llama-3-70B-shaped pruned decoder layer (BASELINE config 5),
+"""Throughput of the Llama-3-70B-shaped pruned decoder layer (the tensor-parallel benchmark case),
 tensor-parallel over the ranks of one node.
 
     python -m dpk_b200.perf_layer                                   # 1 GPU

@@ -238,4 +238,6 @@ if __name__ == "__main__":
     if len(sys.argv) > 2 and sys.argv[2] == "router":
         router_fixture(sys.argv[1])
     else:
-        main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+        if len(sys.argv) < 2:
+            sys.exit("usage: make_golden.py /path/to/reference [router]")
+        main(sys.argv[1])

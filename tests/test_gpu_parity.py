@@ -180,7 +180,7 @@ def test_ffn_golden_and_config1(ops):
                        dev(z["mask"]))
     assert_rel(y, z["down"])
 
-    # config 1: hidden 1024, intermediate 4096 as 32 groups of 128, 512 tokens, top-16
+    # the CPU-runnable benchmark case: hidden 1024, intermediate 4096 as 32 groups of 128, 512 tokens, top-16
     g = seeded(17)
     x = bf16r(torch.randn(1, 512, 1024, generator=g))
     wg = bf16r(torch.randn(4096, 1024, generator=g) * 0.02)
@@ -886,7 +886,7 @@ def test_rope_in_place_without_cache_d128_fp16(ops):
         assert ((got.float().cpu() - want).abs() <= want.abs() * 2 ** -11 + 1e-4).all()
 
 
-@pytest.mark.parametrize("M,H,I,NG,keep", [(64, 4096, 14336, 112, 56),     # config 4 decode step
+@pytest.mark.parametrize("M,H,I,NG,keep", [(64, 4096, 14336, 112, 56),     # the decode-step benchmark case
                                            (1, 256, 512, 4, 2),
                                            (17, 512, 1024, 16, 5),        # 64-channel groups
                                            (128, 384, 640, 5, 3),         # full 128 tokens, odd tiles
