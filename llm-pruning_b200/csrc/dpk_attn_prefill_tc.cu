@@ -100,6 +100,13 @@ __device__ __forceinline__ float tc_exp2(float x)
     return y;
 }
 
+__device__ __forceinline__ float tc_max3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 template <int D>
 struct TcSmem {
     static constexpr int kQBytes = kTcBM * D * 2;
@@ -254,14 +261,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                     if (kidx < lp || kidx > lim) sv[i] = __float_as_uint(-INFINITY);
                 }
             }
-            // row maximum with four independent chains
+            // row maximum with four independent chains of three-input maxima
             float t0 = -INFINITY, t1 = -INFINITY, t2 = -INFINITY, t3 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < kTcBN; i += 4) {
-                t0 = fmaxf(t0, __uint_as_float(sv[i]));
-                t1 = fmaxf(t1, __uint_as_float(sv[i + 1]));
-                t2 = fmaxf(t2, __uint_as_float(sv[i + 2]));
-                t3 = fmaxf(t3, __uint_as_float(sv[i + 3]));
+            for (int i = 0; i < kTcBN; i += 8) {
+                t0 = tc_max3(t0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+                t1 = tc_max3(t1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+                t2 = tc_max3(t2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
+                t3 = tc_max3(t3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
             }
             const float tmax = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3));
             // lazy reference update: move only when the maximum grew by more than 2^8
@@ -280,18 +287,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 
             // P = exp2(scale*S - ref) (masked entries are -inf -> 0), packed to half precision
             uint32_t pk[kTcBN / 2];
-            float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
+            // packed fp32 arithmetic (two values per instruction) for the scaling and the row sum
+            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+            const float2 nref2 = make_float2(-ref, -ref);
+            float2 ra = make_float2(0.f, 0.f), rb = make_float2(0.f, 0.f);
 #pragma unroll
             for (int i = 0; i < kTcBN; i += 4) {
-                const float p0 = tc_exp2(fmaf(__uint_as_float(sv[i]), p.scale_log2, -ref));
-                const float p1 = tc_exp2(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -ref));
-                const float p2 = tc_exp2(fmaf(__uint_as_float(sv[i + 2]), p.scale_log2, -ref));
-                const float p3 = tc_exp2(fmaf(__uint_as_float(sv[i + 3]), p.scale_log2, -ref));
-                r0 += p0; r1 += p1; r2 += p2; r3 += p3;
-                pk[i >> 1] = pack_half2<kBf16>(p0, p1);
-                pk[(i >> 1) + 1] = pack_half2<kBf16>(p2, p3);
+                const float2 a = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])),
+                                            sc2, nref2);
+                const float2 b = __ffma2_rn(make_float2(__uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3])),
+                                            sc2, nref2);
+                const float2 pa = make_float2(tc_exp2(a.x), tc_exp2(a.y));
+                const float2 pb = make_float2(tc_exp2(b.x), tc_exp2(b.y));
+                ra = __fadd2_rn(ra, pa);
+                rb = __fadd2_rn(rb, pb);
+                pk[i >> 1] = pack_half2<kBf16>(pa.x, pa.y);
+                pk[(i >> 1) + 1] = pack_half2<kBf16>(pb.x, pb.y);
             }
-            const float rs = (r0 + r1) + (r2 + r3);
+            const float rs = (ra.x + ra.y) + (rb.x + rb.y);
             l_sum = l_sum * alpha + rs;
 
             // O may only be rescaled once the previous P V has finished (rare: the reference
@@ -446,9 +459,9 @@ static int launch_prefill_tc(const CUtensorMap& tmK, const CUtensorMap& tmV, con
                              cudaStream_t s)
 {
     constexpr size_t smem = TcSmem<D>::kTotal;
+    dim3 grid(p.Hq, (p.Tq + kTcBM - 1) / kTcBM, p.B);
     DPK_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<D, kBf16>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid(p.Hq, (p.Tq + kTcBM - 1) / kTcBM, p.B);
     attn_prefill_tc_kernel<D, kBf16><<<grid, kTcThreads, smem, s>>>(tmK, tmV, p);
     DPK_CUDA(cudaGetLastError());
     return DPK_OK;
