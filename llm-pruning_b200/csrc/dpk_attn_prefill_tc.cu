@@ -28,7 +28,12 @@
 namespace dpk {
 
 constexpr int kTcBM = 128;        // query rows per CTA
-constexpr int kTcBN = 64;         // keys per tile
+#ifndef DPK_ATTN_BN
+#define DPK_ATTN_BN 64
+#endif
+constexpr int kTcBN = DPK_ATTN_BN;          // keys per tile
+constexpr int kTcSBuf = 128 / kTcBN;        // score buffers in TMEM and K/V stages in shared memory
+static_assert(kTcBN == 64 || kTcBN == 32, "tile width");
 constexpr int kTcThreads = 192;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 constexpr int kTcTmemCols = 256;            // 2 x 64 (S) + up to 128 (O)
@@ -73,6 +78,20 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
           "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
         : "memory");
 }
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&v)[16])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        :
+        : "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
+          "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]),
+          "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+// P of one tile: as many 32-bit columns as the tile has key pairs
+__device__ __forceinline__ void tmem_st_p(uint32_t taddr, const uint32_t (&v)[32]) { tmem_st_32x32b_x32(taddr, v); }
+__device__ __forceinline__ void tmem_st_p(uint32_t taddr, const uint32_t (&v)[16]) { tmem_st_32x32b_x16(taddr, v); }
 __device__ __forceinline__ void tmem_st_wait()
 {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -114,9 +133,9 @@ struct TcSmem {
     static constexpr int kVBytes = kTcBN * D * 2;      // one V stage
     static constexpr int kOffQ = 0;
     static constexpr int kOffK = kOffQ + kQBytes;
-    static constexpr int kOffV = kOffK + 2 * kKBytes;
-    static constexpr int kOffBar = kOffV + 2 * kVBytes;
-    static constexpr int kTotal = kOffBar + 16 * 8 + 16;   // base must be 1024-byte aligned
+    static constexpr int kOffV = kOffK + kTcSBuf * kKBytes;
+    static constexpr int kOffBar = kOffV + kTcSBuf * kVBytes;
+    static constexpr int kTotal = kOffBar + 30 * 8 + 16;   // base must be 1024-byte aligned
 };
 
 template <int D, bool kBf16>
@@ -132,14 +151,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     uint8_t* sV = smem + L::kOffV;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBar);
     uint64_t* q_full = bars + 0;
-    uint64_t* k_full = bars + 1;      // [2]
-    uint64_t* v_full = bars + 3;      // [2]
-    uint64_t* k_empty = bars + 5;     // [2]
-    uint64_t* v_empty = bars + 7;     // [2]
-    uint64_t* s_full = bars + 9;      // [2]
-    uint64_t* p_full = bars + 11;
-    uint64_t* pv_done = bars + 12;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    uint64_t* k_full = bars + 1;      // [kTcSBuf]
+    uint64_t* v_full = bars + 5;      // [kTcSBuf]
+    uint64_t* k_empty = bars + 9;     // [kTcSBuf]
+    uint64_t* v_empty = bars + 13;    // [kTcSBuf]
+    uint64_t* s_full = bars + 17;     // [kTcSBuf]
+    // one barrier per score buffer, not one per kernel: a warp role that runs ahead (the softmax
+    // warps have up to kTcSBuf score tiles waiting for them) can then never complete two phases of
+    // a barrier before the other side has looked at the first -- which a parity wait cannot tell
+    // from "not completed yet"
+    uint64_t* p_full = bars + 21;     // [kTcSBuf]
+    uint64_t* pv_done = bars + 25;    // [kTcSBuf]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 30);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -180,15 +203,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 
     if (warp == 4 && lane == 0) {
         mbar_init(q_full, 128);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kTcSBuf; ++s) {
             mbar_init(&k_full[s], 1);
             mbar_init(&v_full[s], 1);
             mbar_init(&k_empty[s], 1);
             mbar_init(&v_empty[s], 1);
             mbar_init(&s_full[s], 1);
+            mbar_init(&p_full[s], 128);
+            mbar_init(&pv_done[s], 1);
         }
-        mbar_init(p_full, 128);
-        mbar_init(pv_done, 1);
         *abort_flag = 0;
         mbar_init_fence();
         tma_prefetch_desc(&tmK);
@@ -199,7 +222,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s0 = tmem_base;            // S buffers: columns [0,64), [64,128)
+    const uint32_t tmem_s0 = tmem_base;            // S buffers: kTcSBuf x kTcBN columns in [0,128)
     const uint32_t tmem_o = tmem_base + 128;       // O: columns [128, 128 + D)
 
     if (warp < 4) {
@@ -231,8 +254,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         float l_sum = 0.f;
         bool alive = true;
         for (int j = 0; j < ntiles; ++j) {
-            const int sb = j & 1;
-            const bool got = mbar_wait(&s_full[sb], (j >> 1) & 1, abort_flag, p.status,
+            const int sb = j % kTcSBuf;
+            const bool got = mbar_wait(&s_full[sb], (j / kTcSBuf) & 1, abort_flag, p.status,
                                        DPK_DEV_TIMEOUT_TMEM_FULL);
             if (!__all_sync(0xffffffffu, got)) { alive = false; break; }
             tc_fence_after_sync();
@@ -246,13 +269,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 
             // the whole score row of this tile (64 values) stays in registers
             uint32_t sv[kTcBN];
-            {
+            if constexpr (kTcBN == 64) {
                 uint32_t a32[32], b32[32];
                 tmem_ld_32x32b_x32(ts, a32);
                 tmem_ld_32x32b_x32(ts + 32, b32);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) { sv[i] = a32[i]; sv[32 + i] = b32[i]; }
+                for (int i = 0; i < 32; ++i) { sv[i] = a32[i]; sv[(32 + i) % kTcBN] = b32[i]; }
+            } else {
+                uint32_t a32[32];
+                tmem_ld_32x32b_x32(ts, a32);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sv[i] = a32[i];
             }
             if (need_mask) {
 #pragma unroll
@@ -310,8 +339,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             // O may only be rescaled once the previous P V has finished (rare: the reference
             // maximum of some row of this warp moved)
             if (j > 0 && __any_sync(0xffffffffu, moved)) {
-                const bool ok2 = mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status,
-                                           DPK_DEV_TIMEOUT_TMEM_EMPTY);
+                const bool ok2 = mbar_wait(&pv_done[(j - 1) % kTcSBuf], ((j - 1) / kTcSBuf) & 1, abort_flag,
+                                           p.status, DPK_DEV_TIMEOUT_TMEM_EMPTY);
                 if (!__all_sync(0xffffffffu, ok2)) { alive = false; break; }
                 tc_fence_after_sync();
 #pragma unroll 1
@@ -328,16 +357,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             }
             // P replaces the first 32 columns of this tile's S buffer in TMEM (two keys per
             // 32-bit column); the P V UMMA reads its A operand from there
-            tmem_st_32x32b_x32(ts, pk);
+            tmem_st_p(ts, pk);
             tmem_st_wait();
             tc_fence_before_sync();
-            mbar_arrive(p_full);
+            mbar_arrive(&p_full[sb]);
         }
 
         // ---- epilogue: O / l, scattered to the token's row ---------------------------------
         if (alive && ntiles > 0) {
-            const bool ok3 = mbar_wait(pv_done, (ntiles - 1) & 1, abort_flag, p.status,
-                                       DPK_DEV_TIMEOUT_TMEM_EMPTY);
+            const bool ok3 = mbar_wait(&pv_done[(ntiles - 1) % kTcSBuf], ((ntiles - 1) / kTcSBuf) & 1,
+                                       abort_flag, p.status, DPK_DEV_TIMEOUT_TMEM_EMPTY);
             alive = __all_sync(0xffffffffu, ok3);
             tc_fence_after_sync();
         }
@@ -374,8 +403,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             const int row_base = b * p.Tk;
             const int col_base = kvh * D;
             for (int j = 0; j < ntiles; ++j) {
-                const int s = j & 1;
-                const uint32_t ph = ((j >> 1) & 1) ^ 1;
+                const int s = j % kTcSBuf;
+                const uint32_t ph = ((j / kTcSBuf) & 1) ^ 1;
                 const int kv0 = kv_begin + j * kTcBN;
                 if (!mbar_wait(&k_empty[s], ph, abort_flag, p.status, DPK_DEV_TIMEOUT_EMPTY)) break;
                 mbar_arrive_expect_tx(&k_full[s], L::kKBytes);
@@ -399,8 +428,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             const uint32_t idesc_o = umma_idesc_f16(kBf16 ? 1 : 0, kTcBM, D) | (1u << 16);
             bool ok = mbar_wait(q_full, 0, abort_flag, p.status, DPK_DEV_TIMEOUT_FULL);
             auto issue_s = [&](int j) -> bool {
-                const int s = j & 1;
-                if (!mbar_wait(&k_full[s], (j >> 1) & 1, abort_flag, p.status, DPK_DEV_TIMEOUT_FULL))
+                const int s = j % kTcSBuf;
+                if (!mbar_wait(&k_full[s], (j / kTcSBuf) & 1, abort_flag, p.status, DPK_DEV_TIMEOUT_FULL))
                     return false;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_s0 + s * kTcBN;
@@ -417,17 +446,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                 umma_commit(&k_empty[s]);
                 return true;
             };
-            if (ok) ok = issue_s(0);
-            if (ok && ntiles > 1) ok = issue_s(1);
+            for (int j = 0; ok && j < kTcSBuf && j < ntiles; ++j) ok = issue_s(j);
             for (int j = 0; ok && j < ntiles; ++j) {
-                const int s = j & 1;
-                if (!mbar_wait(p_full, j & 1, abort_flag, p.status, DPK_DEV_TIMEOUT_FULL) ||
-                    !mbar_wait(&v_full[s], (j >> 1) & 1, abort_flag, p.status, DPK_DEV_TIMEOUT_FULL)) {
+                const int s = j % kTcSBuf;
+                if (!mbar_wait(&p_full[s], (j / kTcSBuf) & 1, abort_flag, p.status, DPK_DEV_TIMEOUT_FULL) ||
+                    !mbar_wait(&v_full[s], (j / kTcSBuf) & 1, abort_flag, p.status, DPK_DEV_TIMEOUT_FULL)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
-                // 64 keys = 4 steps of 16: B advances 16 key rows = 2048 bytes; the d blocks of V
+                // kTcBN keys in steps of 16: B advances 16 key rows = 2048 bytes; the d blocks of V
                 // are kTcBN*128 bytes apart
 #pragma unroll
                 for (int k = 0; k < kTcBN / 16; ++k) {
@@ -437,9 +465,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                     umma_f16_ts(tmem_o, tmem_s0 + s * kTcBN + k * 8, bdesc, idesc_o,
                                 (j | k) != 0 ? 1u : 0u);
                 }
-                umma_commit(pv_done);
+                umma_commit(&pv_done[s]);
                 umma_commit(&v_empty[s]);
-                if (j + 2 < ntiles) ok = issue_s(j + 2);
+                if (j + kTcSBuf < ntiles) ok = issue_s(j + kTcSBuf);
             }
         }
     }
