@@ -87,3 +87,59 @@ class TensorParallelFFN:
         if self.world > 1:
             dist.all_reduce(y, group=self.pg)
         return y
+
+
+def owner_block_sum(partial: torch.Tensor, process_group: Optional[dist.ProcessGroup] = None,
+                    residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The data movement of the fused row-parallel sum (:mod:`dpk_b200.peer`) written with plain
+    point-to-point messages, for ranks that cannot map each other's memory (other nodes, CPU
+    ranks): rows are owned in contiguous blocks of whole 128-token windows
+    (:func:`dpk_b200.peer.rows_per_owner`); every rank sends each owner its partial rows of that
+    owner's block, the owner adds the ``world`` contributions in rank order (fp32, plus the
+    residual rows when given), rounds once and sends the finished rows to everyone.
+    ``partial``: ``[M, N]``.  Returns the summed ``[M, N]`` (same on every rank, bit for bit)."""
+    from .peer import rows_per_owner
+    world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+    rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+    M, N = partial.shape
+    R = rows_per_owner(M, world)
+    block = lambda o: slice(min(o * R, M), min((o + 1) * R, M))
+    mine = block(rank)
+    # first half: partial rows to their owners
+    got = [None] * world
+    reqs = []
+    for o in range(world):
+        if o == rank or block(o).start == block(o).stop:
+            continue
+        reqs.append(dist.isend(partial[block(o)].contiguous(), o, group=process_group))
+    for src in range(world):
+        if src == rank or mine.start == mine.stop:
+            continue
+        got[src] = torch.empty_like(partial[mine])
+        reqs.append(dist.irecv(got[src], src, group=process_group))
+    for r in reqs:
+        r.wait()
+    got[rank] = partial[mine]
+    out = torch.empty_like(partial)
+    if mine.start != mine.stop:
+        acc = torch.zeros(partial[mine].shape, dtype=torch.float32, device=partial.device)
+        for src in range(world):                       # rank order: the same sum on every owner
+            acc += got[src].to(torch.float32)
+        if residual is not None:
+            acc += residual[mine].to(torch.float32)
+        out[mine] = acc.to(partial.dtype)
+    # second half: finished rows to everyone
+    reqs = []
+    for dst in range(world):
+        if dst != rank and mine.start != mine.stop:
+            reqs.append(dist.isend(out[mine].contiguous(), dst, group=process_group))
+    bufs = {}
+    for o in range(world):
+        if o != rank and block(o).start != block(o).stop:
+            bufs[o] = torch.empty_like(out[block(o)])
+            reqs.append(dist.irecv(bufs[o], o, group=process_group))
+    for r in reqs:
+        r.wait()
+    for o, buf in bufs.items():
+        out[block(o)] = buf
+    return out

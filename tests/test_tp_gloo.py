@@ -54,7 +54,17 @@ def _worker(rank, world, port, ret):
         dist.all_reduce(part)
         want_o = O.attention_prefill(q, k, v, am).flatten(2) @ wo.T
         ok_attn = torch.allclose(part, want_o, atol=1e-4, rtol=1e-4)
-        ret[rank] = (ok_ffn, ok_attn)
+        # the fused row-parallel sum's data movement (owner blocks of whole 128-token windows,
+        # contributions added in rank order, finished rows to everyone) as point-to-point messages
+        Mrows = 300
+        part2 = torch.randn(Mrows, H, generator=torch.Generator().manual_seed(11 + rank)).to(torch.bfloat16)
+        res2 = torch.randn(Mrows, H, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+        summed = tp.owner_block_sum(part2, residual=res2)
+        total = part2.float().clone()
+        dist.all_reduce(total)
+        want_sum = (total + res2.float()).to(torch.bfloat16)
+        ok_sum = torch.equal(summed, want_sum)
+        ret[rank] = (ok_ffn, ok_attn, ok_sum)
     finally:
         dist.destroy_process_group()
 
@@ -64,7 +74,7 @@ def test_two_rank_partition_and_allreduce():
     with mp.Manager() as mgr:
         ret = mgr.dict()
         mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
-        assert dict(ret) == {0: (True, True), 1: (True, True)}
+        assert dict(ret) == {0: (True, True, True), 1: (True, True, True)}
 
 
 def test_partition_helpers():
