@@ -46,6 +46,24 @@ def owner_of_row(row: int, M: int, world: int) -> int:
     return row // rows_per_owner(M, world)
 
 
+def half_split(M: int, world: int, width: int, part: Optional[int]):
+    """``(row0, rows, staging offset in elements)`` of the whole call (``part`` None) or of its
+    first / second half (0 / 1).  The first half ends on a window boundary; each half is its own
+    ownership split, and the second half's slabs start where the first half's end."""
+    if part is None:
+        return 0, M, 0
+    M0 = min(M, ((M + 1) // 2 + WINDOW - 1) // WINDOW * WINDOW)
+    if part == 0:
+        return 0, M0, 0
+    return M0, M - M0, world * rows_per_owner(M0, world) * width
+
+
+def staging_rows(max_rows: int, world: int) -> int:
+    """Rows per slab a staging buffer is sized for: the share of ``max_rows`` plus two windows,
+    which covers the separate rounding of the two halves."""
+    return rows_per_owner(max_rows, world) + 2 * WINDOW
+
+
 def slab_offset(row: int, M: int, world: int, source_rank: int, ld: int) -> int:
     """Element offset, inside the owner's staging buffer, of ``row`` as sent by
     ``source_rank`` (layout ``[world, rows_per_owner, ld]``)."""
@@ -92,8 +110,7 @@ class RowParallelSum:
     # ---- construction -----------------------------------------------------------------
     @staticmethod
     def _sizes(world: int, max_rows: int, width: int):
-        # two halves round their shares up separately: two more windows per rank cover both
-        R = rows_per_owner(max_rows, world) + 2 * WINDOW
+        R = staging_rows(max_rows, world)
         return R, world * R * width * 2
 
     @classmethod
@@ -180,13 +197,7 @@ class RowParallelSum:
 
     # ---- the two kernels ------------------------------------------------------------------
     def _part(self, M: int, part: Optional[int]):
-        """Rows ``[row0, row0+rows)`` of a call and where their staging slabs start (elements)."""
-        if part is None:
-            return 0, M, 0
-        M0 = min(M, ((M + 1) // 2 + WINDOW - 1) // WINDOW * WINDOW)
-        if part == 0:
-            return 0, M0, 0
-        return M0, M - M0, self.world * rows_per_owner(M0, self.world) * self.width
+        return half_split(M, self.world, self.width, part)
 
     def scatter(self, A2: torch.Tensor, W: torch.Tensor, row_bits: torch.Tensor,
                 win_bits: torch.Tensor, NG: int, part: Optional[int] = None) -> None:

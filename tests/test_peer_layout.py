@@ -50,3 +50,17 @@ def test_scatter_then_reduce_gather_is_the_sum(M, world, ld):
     want = partial.sum(axis=0)
     for dst in range(world):
         np.testing.assert_allclose(out[dst], want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("M,world", [(1024, 2), (2100, 4), (4500, 8), (16384, 8), (8192, 8), (513, 2), (100000, 8)])
+def test_two_halves_cover_the_rows_and_fit_the_staging_buffer(M, world):
+    width = 8
+    r0, n0, s0 = peer.half_split(M, world, width, 0)
+    r1, n1, s1 = peer.half_split(M, world, width, 1)
+    assert (r0, s0) == (0, 0) and r1 == n0 and n0 + n1 == M
+    assert n0 % peer.WINDOW == 0 or n1 == 0                 # the cut is on a window boundary
+    # the second half's slabs start right after the first half's and both fit what connect() sizes
+    assert s1 == world * peer.rows_per_owner(n0, world) * width
+    end = s1 + world * peer.rows_per_owner(max(n1, 1), world) * width
+    assert end <= world * peer.staging_rows(M, world) * width
+    assert peer.half_split(M, world, width, None) == (0, M, 0)
