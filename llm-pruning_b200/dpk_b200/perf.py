@@ -23,7 +23,7 @@ import sys
 
 import torch
 
-from . import ops
+from . import _native, ops
 from .ffn import RoutedFFN
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -240,11 +240,44 @@ def run_router_norm(args):
             "torch_ms": dms, "speedup_vs_torch": dms / ms}
 
 
+def run_gemm_k_scatter(args):
+    """The tensor-parallel down projection of one rank (70B-shaped layer split 4 ways: 56 of 224
+    channel groups) with its epilogue storing into the owners' staging slabs -- all four ranks'
+    buffers live on this GPU (``RowParallelSum.emulate``), so the stores are local; what is
+    measured is the kernel itself against the plain ``gemm_k`` on the same operands."""
+    from .peer import RowParallelSum
+    world, M, N, NG = 4, args.tokens or 8192, 8192, 56
+    K = NG * 128
+    gen = torch.Generator(device="cuda").manual_seed(SEED)
+    bf = torch.bfloat16
+    a = torch.randn(M, K, generator=gen, device="cuda").to(bf)
+    w = (torch.randn(N, K, generator=gen, device="cuda") * 0.02).to(bf)
+    mask = topk_mask((1, M, NG), NG // 2, gen)[0]
+    ranks = RowParallelSum.emulate(world, M, N, bf, torch.device("cuda"))
+    words = (NG + 31) // 32
+    rb = torch.empty((M, words), dtype=torch.int32, device="cuda")
+    wb = torch.empty(((M + 127) // 128, words), dtype=torch.int32, device="cuda")
+    m8 = mask.to(torch.uint8).contiguous()
+    _native.check(_native.load().dpk_mask_pack(m8.data_ptr(), M, NG, rb.data_ptr(), wb.data_ptr(), None))
+    ms, lo, hi = time_ms(lambda: ranks[1].scatter(a, w, rb, wb, NG), args.reps)
+    d = torch.empty(1, M, N, dtype=bf, device="cuda")
+    pms, _, _ = time_ms(lambda: ops.gemm_k(a[None], w, mask[None], D=d), args.reps)
+    peak_tf, _, src = peaks()
+    executed = 2.0 * N * K * M            # every window visits every group at a 50 % keep ratio
+    ach = executed / (ms * 1e-3) / 1e12
+    return {"kernel": "gemm_k_scatter", "workload": f"M={M} N={N} K={K} ({NG}x128, top-{NG // 2}), "
+            f"rank 1 of {world} emulated on one GPU", "ms": ms, "ms_q20": lo, "ms_q80": hi,
+            "plain_gemm_k_call_ms": pms,
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s",
+                         "frac": ach / peak_tf, "peak_source": src + " sustained bf16",
+                         "note": "executed flops (the masked formulation runs 2x the algorithmic ones)"}}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--kernel", required=True,
                     choices=["attention_prefill", "attention_decode", "ffn", "ffn_decode",
-                             "gemm_mn", "gemm_k", "router_norm"])
+                             "gemm_mn", "gemm_k", "router_norm", "gemm_k_scatter"])
     ap.add_argument("--hidden", type=int, default=0, help="override the hidden size (router_norm)")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--tokens", type=int, default=0, help="override the token / KV length")
@@ -261,6 +294,8 @@ def main(argv=None):
         res = run_ffn(args, decode=True)
     elif args.kernel == "router_norm":
         res = run_router_norm(args)
+    elif args.kernel == "gemm_k_scatter":
+        res = run_gemm_k_scatter(args)
     else:
         res = run_gemm(args, args.kernel)
     status = ops.device_status()
