@@ -5,8 +5,10 @@
  * TVM-FFI `Host::run(TensorView...)` functions.  Every entry point takes raw
  * device pointers, sizes, element strides and a CUDA stream, launches on that
  * stream without synchronising, allocates nothing and keeps no state besides
- * cached device properties.  All return 0 on success or one of the DPK_ERR_*
- * codes; dpk_last_error() then holds a message (thread local).
+ * cached device properties -- with one exception: dpk_peer_alloc / dpk_peer_free
+ * (tensor-parallel set-up, not on any per-step path) allocate and release the
+ * device buffer that peers map through CUDA IPC.  All return 0 on success or one
+ * of the DPK_ERR_* codes; dpk_last_error() then holds a message (thread local).
  *
  * Conventions
  *   - "half" tensors are fp16 or bf16 as selected by `dtype` (DPK_F16 / DPK_BF16),
@@ -227,8 +229,13 @@ int dpk_ffn_swiglu(const void* x, const void* Wg, const void* Wu, const void* Wd
  * Prefill attention over the active query rows of each head group (reference:
  * Attention_Head_V3_Host::run, DynamicPruningKernels/include/attention_prefill/v3/
  * sm12x.cuh:25-169; host wrapper python/attention_prefill/jit.py:223-284).
- *   Q,O [B,Tq,Hq,D], K,V [B,Tk,Hk,D] contiguous; group g = query heads
+ *   Q,O [B,Tq,Hq,D], K,V [B,Tk,Hk,D]; group g = query heads
  *   [g*Hq/NG, (g+1)*Hq/NG); query head h reads KV head h / (Hq/Hk).
+ *   O is packed.  Q, K and V keep the heads of a token back to back but may be strided
+ *   beyond that (a slice of a fused projection's output, a view of a KV cache with spare
+ *   capacity): q_token_stride / q_batch_stride and kv_token_stride / kv_batch_stride (K and V
+ *   alike) are in elements, multiples of 8, 0 = packed.  The reference takes DLPack views
+ *   with strides {.., D, 1} the same way (sm12x.cuh:88-99).
  *   sorted_indices [B,Tq,NG] int64 (token index within the batch row), counts [B,NG].
  *   leftpad: optional [B] uint32 (keys k < leftpad[b] excluded) or NULL.
  *   causal: keys k <= q + causal_shift are visible (0 = top-left alignment).
@@ -238,7 +245,8 @@ int dpk_ffn_swiglu(const void* x, const void* Wg, const void* Wu, const void* Wd
 int dpk_attn_prefill(const void* Q, const void* K, const void* V, const int64_t* sorted_indices,
                      const int32_t* counts, const uint32_t* leftpad, void* O, int B, int Tq,
                      int Tk, int Hq, int Hk, int D, int NG, float scale, int causal,
-                     int causal_shift, int dtype, void* stream);
+                     int causal_shift, int dtype, int64_t q_token_stride, int64_t q_batch_stride,
+                     int64_t kv_token_stride, int64_t kv_batch_stride, void* stream);
 
 /* Bytes of scratch dpk_attn_decode needs. */
 size_t dpk_attn_decode_workspace_bytes(int B, int Tk, int Hq, int Hk, int D, int NG);
@@ -249,12 +257,15 @@ size_t dpk_attn_decode_workspace_bytes(int B, int Tk, int Hq, int Hk, int D, int
  * DynamicPruningKernels/include/attention_decode/v0/sm12x.cuh:23-198; host wrapper
  * python/attention_decode/jit.py:201-261).  KV heads none of whose query-head groups
  * are active for a sequence are never read.
- *   Q,O [B,1,Hq,D], K,V [B,Tk,Hk,D], mask [B,NG] bytes, leftpad optional [B] uint32.
+ *   Q,O [B,1,Hq,D] packed, K,V [B,Tk,Hk,D], mask [B,NG] bytes, leftpad optional [B] uint32.
+ *   kv_token_stride / kv_batch_stride (elements, multiples of 8, 0 = packed): K and V may be
+ *   the first Tk rows of a [B,capacity,Hk,D] cache, read in place.
  * O is fully written (zeros for inactive groups).
  */
 int dpk_attn_decode(const void* Q, const void* K, const void* V, const uint8_t* mask,
                     const uint32_t* leftpad, void* O, int B, int Tk, int Hq, int Hk, int D, int NG,
-                    float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream);
+                    float scale, int dtype, int64_t kv_token_stride, int64_t kv_batch_stride,
+                    void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * The same FFN for at most 128 tokens (decode steps), as two launches without any routing
@@ -298,11 +309,14 @@ int dpk_router_norm(const void* x, int64_t ldx, const void* gamma, float eps, co
  *   q [B,T,Hq,D] rotated in place; k [B,T,Hk,D]; v [B,T,Hk,D]; cos, sin [T,D] (batch stride
  *   0) or [B,T,D]; k_cache, v_cache [B,capacity,Hk,D]: rows past_len .. past_len+T-1 receive
  *   the rotated k and v.  Without caches (both NULL) k is rotated in place.
+ *   q_token_stride / kv_token_stride (elements, multiples of 8, 0 = packed): q, and k and v,
+ *   may be column slices of one fused projection output [B*T, width].
  * fp32 arithmetic, one rounding.  D a multiple of 16.
  */
 int dpk_rope_append(void* q, void* k, const void* v, const void* cos, const void* sin,
                     int64_t cs_batch_stride, void* k_cache, void* v_cache, int B, int T, int Hq,
-                    int Hk, int D, int64_t capacity, int64_t past_len, int dtype, void* stream);
+                    int Hk, int D, int64_t capacity, int64_t past_len, int dtype,
+                    int64_t q_token_stride, int64_t kv_token_stride, void* stream);
 
 /* ---- tensor parallel: the row-parallel sum fused into the projection ---------------
  *

@@ -35,6 +35,7 @@ struct DecodeParams {
     float* pO;                // [B, Hq, splits, D]
     float* pML;               // [B, Hq, splits, 2]
     int B, Tk, Hq, Hk, NG;
+    int64_t kv_ts, kv_bs;    // elements between consecutive cached tokens / sequences of K and V
     int splits, split_len;
     float scale_log2;
 };
@@ -124,9 +125,9 @@ attn_decode_kernel(const DecodeParams p)
     }
     cp_async_commit();
 
-    const uint8_t* Kb = p.K + (static_cast<int64_t>(b) * p.Tk * p.Hk + kvh) * ROWB;
-    const uint8_t* Vb = p.V + (static_cast<int64_t>(b) * p.Tk * p.Hk + kvh) * ROWB;
-    const int64_t kv_stride = static_cast<int64_t>(p.Hk) * ROWB;
+    const uint8_t* Kb = p.K + static_cast<int64_t>(b) * p.kv_bs * 2 + static_cast<int64_t>(kvh) * ROWB;
+    const uint8_t* Vb = p.V + static_cast<int64_t>(b) * p.kv_bs * 2 + static_cast<int64_t>(kvh) * ROWB;
+    const int64_t kv_stride = p.kv_ts * 2;
     uint8_t* myPipe = sPipe + warp * WARP_B;
     auto load_tile = [&](int t, int stage) {
         const int kv0 = first_tile + (warp + t * kDecWarps) * kDecBN;
@@ -372,7 +373,8 @@ size_t dpk_attn_decode_workspace_bytes(int B, int Tk, int Hq, int Hk, int D, int
 
 int dpk_attn_decode(const void* Q, const void* K, const void* V, const uint8_t* mask,
                     const uint32_t* leftpad, void* O, int B, int Tk, int Hq, int Hk, int D, int NG,
-                    float scale, int dtype, void* workspace, size_t workspace_bytes, void* stream)
+                    float scale, int dtype, int64_t kv_token_stride, int64_t kv_batch_stride,
+                    void* workspace, size_t workspace_bytes, void* stream)
 {
     DPK_REQUIRE(Q && K && V && O && mask, "NULL tensor");
     DPK_REQUIRE(dtype == DPK_F16 || dtype == DPK_BF16, "dtype must be DPK_F16 or DPK_BF16");
@@ -383,6 +385,10 @@ int dpk_attn_decode(const void* Q, const void* K, const void* V, const uint8_t* 
     DPK_REQUIRE(Hq / Hk <= 16, "more than 16 query heads per KV head are not supported");
     DPK_REQUIRE(B <= 65535 && Hk <= 65535, "grid too large");
     DPK_REQUIRE(aligned16(Q) && aligned16(K) && aligned16(V), "tensors must be 16-byte aligned");
+    const int64_t kv_ts = kv_token_stride ? kv_token_stride : static_cast<int64_t>(Hk) * D;
+    const int64_t kv_bs = kv_batch_stride ? kv_batch_stride : static_cast<int64_t>(Tk) * kv_ts;
+    DPK_REQUIRE(kv_ts >= static_cast<int64_t>(Hk) * D && kv_ts % 8 == 0 && kv_bs % 8 == 0,
+                "K/V strides must cover a token's heads and be multiples of 8 elements (16 bytes)");
     if (B == 0) return DPK_OK;
     size_t need = dpk_attn_decode_workspace_bytes(B, Tk, Hq, Hk, D, NG);
     DPK_REQUIRE(workspace && workspace_bytes >= need, "workspace of %zu bytes needed, %zu given", need,
@@ -396,6 +402,7 @@ int dpk_attn_decode(const void* Q, const void* K, const void* V, const uint8_t* 
     p.mask = mask;
     p.leftpad = leftpad;
     p.B = B; p.Tk = Tk; p.Hq = Hq; p.Hk = Hk; p.NG = NG;
+    p.kv_ts = kv_ts; p.kv_bs = kv_bs;
     p.splits = decode_splits(B, Tk, Hk);
     int len = (Tk + p.splits - 1) / p.splits;
     p.split_len = ((len + 127) / 128) * 128;

@@ -45,6 +45,7 @@ struct PrefillTcParams {
     const int32_t* counts;   // [B, NG]
     const uint32_t* leftpad; // [B] or null
     int B, Tq, Tk, Hq, Hk, NG;
+    int64_t q_ts, q_bs;      // elements between consecutive tokens / batch entries of Q
     float scale_log2;
     int causal, causal_shift;
     int* status;
@@ -235,7 +236,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             for (int r = rsub; r < kTcBM; r += 16) {
                 const int t = token_of(r);
                 const uint8_t* src_row =
-                    t >= 0 ? p.Q + ((static_cast<int64_t>(b) * p.Tq + t) * p.Hq + h) * (D * 2) : p.Q;
+                    t >= 0 ? p.Q + (static_cast<int64_t>(b) * p.q_bs + static_cast<int64_t>(t) * p.q_ts +
+                                    static_cast<int64_t>(h) * D) * 2
+                           : p.Q;
 #pragma unroll
                 for (int kb = 0; kb < KBQ; ++kb) {
                     const uint32_t dst = smem_u32(sQ) + kb * (kTcBM * 128) + r * 128 +
@@ -400,7 +403,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     } else if (warp == 4) {
         // =================== TMA producer: K and V tiles ====================================
         if (lane == 0) {
-            const int row_base = b * p.Tk;
             const int col_base = kvh * D;
             for (int j = 0; j < ntiles; ++j) {
                 const int s = j % kTcSBuf;
@@ -410,14 +412,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                 mbar_arrive_expect_tx(&k_full[s], L::kKBytes);
 #pragma unroll
                 for (int kb = 0; kb < KBQ; ++kb)
-                    tma_load_2d(sK + s * L::kKBytes + kb * (kTcBN * 128), &tmK, &k_full[s],
-                                col_base + kb * 64, row_base + kv0);
+                    tma_load_3d(sK + s * L::kKBytes + kb * (kTcBN * 128), &tmK, &k_full[s],
+                                col_base + kb * 64, kv0, b);
                 if (!mbar_wait(&v_empty[s], ph, abort_flag, p.status, DPK_DEV_TIMEOUT_EMPTY)) break;
                 mbar_arrive_expect_tx(&v_full[s], L::kVBytes);
 #pragma unroll
                 for (int kb = 0; kb < KBQ; ++kb)
-                    tma_load_2d(sV + s * L::kVBytes + kb * (kTcBN * 128), &tmV, &v_full[s],
-                                col_base + kb * 64, row_base + kv0);
+                    tma_load_3d(sV + s * L::kVBytes + kb * (kTcBN * 128), &tmV, &v_full[s],
+                                col_base + kb * 64, kv0, b);
             }
         }
     } else {
@@ -499,14 +501,15 @@ static int launch_prefill_tc(const CUtensorMap& tmK, const CUtensorMap& tmV, con
 int attn_prefill_tc(const void* Q, const void* K, const void* V, const int64_t* sorted_indices,
                     const int32_t* counts, const uint32_t* leftpad, void* O, int B, int Tq, int Tk,
                     int Hq, int Hk, int D, int NG, float scale, int causal, int causal_shift,
-                    int dtype, cudaStream_t s)
+                    int dtype, int64_t q_ts, int64_t q_bs, int64_t kv_ts, int64_t kv_bs, cudaStream_t s)
 {
+    // K and V as [batch][key][Hk*D] maps: a tile that runs past the last key of its batch entry
+    // is zero-filled by the copy engine, whatever lies behind it in memory
     CUtensorMap tmK, tmV;
     const uint64_t cols = static_cast<uint64_t>(Hk) * D;
-    const uint64_t rows = static_cast<uint64_t>(B) * Tk;
-    int rc = make_tmap_2d_sw128(&tmK, K, cols, rows, cols, 64, kTcBN);
+    int rc = make_tmap_3d_sw128(&tmK, K, cols, Tk, B, kv_ts, kv_bs, 64, kTcBN);
     if (rc) return rc;
-    rc = make_tmap_2d_sw128(&tmV, V, cols, rows, cols, 64, kTcBN);
+    rc = make_tmap_3d_sw128(&tmV, V, cols, Tk, B, kv_ts, kv_bs, 64, kTcBN);
     if (rc) return rc;
     PrefillTcParams p;
     p.Q = static_cast<const uint8_t*>(Q);
@@ -515,6 +518,7 @@ int attn_prefill_tc(const void* Q, const void* K, const void* V, const int64_t* 
     p.counts = counts;
     p.leftpad = leftpad;
     p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hk = Hk; p.NG = NG;
+    p.q_ts = q_ts; p.q_bs = q_bs;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.causal = causal ? 1 : 0;
     p.causal_shift = causal_shift;

@@ -59,6 +59,7 @@ struct SmallSmem {
     uint32_t* tmem_slot;
     volatile int* abort_flag;
     int* flag;
+    volatile int* gave_up;     // an epilogue warp's wait ran out: all four leave together
 };
 
 __device__ __forceinline__ SmallSmem small_smem(uint8_t* raw)
@@ -72,6 +73,7 @@ __device__ __forceinline__ SmallSmem small_smem(uint8_t* raw)
     s.tmem_slot = reinterpret_cast<uint32_t*>(s.tempty + 2);
     s.abort_flag = reinterpret_cast<volatile int*>(s.tmem_slot + 1);
     s.flag = reinterpret_cast<int*>(s.tmem_slot + 2);
+    s.gave_up = reinterpret_cast<volatile int*>(s.tmem_slot + 3);
     return s;
 }
 
@@ -116,6 +118,7 @@ ffn_small_kernel(const __grid_constant__ CUtensorMap tmTok, const __grid_constan
             mbar_init(&sm.tempty[b], 128);
         }
         *sm.abort_flag = 0;
+        *sm.gave_up = 0;
         mbar_init_fence();
     }
     if (warp == 5) tmem_alloc(sm.tmem_slot, kSmTmemCols);
@@ -139,33 +142,46 @@ ffn_small_kernel(const __grid_constant__ CUtensorMap tmTok, const __grid_constan
             const int ab = acc_it & 1;
             const bool got = mbar_wait(&sm.tfull[ab], (acc_it >> 1) & 1, sm.abort_flag, p.status,
                                        DPK_DEV_TIMEOUT_TMEM_FULL);
-            if (!__all_sync(0xffffffffu, got)) break;
-            tc_fence_after_sync();
-            // partial sums of this part -> fp32 buffer (a warp adds 32 consecutive floats)
+            // A wait that ran out must not let this warp leave on its own: the other three would
+            // sit at the named barriers below for good.  The warp only records the failure and
+            // skips its share of the work; all four warps pass the three barriers of this
+            // iteration, read the same flag between the second and the third, and leave together.
+            // (gave_up is written before the first barrier and read after the second, so a
+            // write of the next iteration cannot reach a reader of this one.)
+            const bool warp_ok = __all_sync(0xffffffffu, got);
             const int block = kUp ? tile >> 1 : tile;
-            const bool second = kUp && (tile & 1);          // an up tile: its sums live past the gate sums
-            float* dst = p.acc + (second ? static_cast<int64_t>(p.blocks) * 128 : 0) +
-                         static_cast<int64_t>(block) * 128 + row;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) +
-                                   static_cast<uint32_t>(ab * NT);
-            for (int c = 0; c < NT; c += 16) {
-                uint32_t v[16];
-                tmem_ld_32x32b_x16(taddr + c, v);
-                tmem_ld_wait();
+            if (warp_ok) {
+                tc_fence_after_sync();
+                // partial sums of this part -> fp32 buffer (a warp adds 32 consecutive floats)
+                const bool second = kUp && (tile & 1);          // an up tile: its sums live past the gate sums
+                float* dst = p.acc + (second ? static_cast<int64_t>(p.blocks) * 128 : 0) +
+                             static_cast<int64_t>(block) * 128 + row;
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) +
+                                       static_cast<uint32_t>(ab * NT);
+                for (int c = 0; c < NT; c += 16) {
+                    uint32_t v[16];
+                    tmem_ld_32x32b_x16(taddr + c, v);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int t = 0; t < 16; ++t)
-                    if (c + t < p.M) atomicAdd(dst + static_cast<int64_t>(c + t) * p.acc_ld, __uint_as_float(v[t]));
+                    for (int t = 0; t < 16; ++t)
+                        if (c + t < p.M) atomicAdd(dst + static_cast<int64_t>(c + t) * p.acc_ld, __uint_as_float(v[t]));
+                }
+                tc_fence_before_sync();
+                mbar_arrive(&sm.tempty[ab]);
+            } else if (lane == 0) {
+                *sm.gave_up = 1;
             }
-            tc_fence_before_sync();
-            mbar_arrive(&sm.tempty[ab]);
             // count the finished k-blocks of the block; whoever completes it runs its epilogue
             const int full_count = kUp ? 2 * KB : KB;
             __threadfence();
             named_barrier_128(1);
-            if (threadIdx.x == 0) *sm.flag = atomicAdd(p.counters + block, k1 - k0) + (k1 - k0);
+            if (threadIdx.x == 0)
+                *sm.flag = *sm.gave_up ? -1 : atomicAdd(p.counters + block, k1 - k0) + (k1 - k0);
             named_barrier_128(1);
-            const bool last = *sm.flag == full_count;
+            const int seen = *sm.flag;
             named_barrier_128(1);              // everyone has read the flag before it is reused
+            if (seen < 0) break;               // the same value in all 128 threads
+            const bool last = seen == full_count;
             if (!last) continue;
             __threadfence();
             // The block's epilogue: a thread takes (token, 4 channels) pieces -- a warp covers the 128

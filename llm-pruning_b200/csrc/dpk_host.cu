@@ -61,6 +61,34 @@ static int make_tmap(CUtensorMap* map, const void* base, uint64_t cols, uint64_t
     return DPK_OK;
 }
 
+int make_tmap_3d_sw128(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
+                       uint64_t batches, uint64_t row_stride_elems, uint64_t batch_stride_elems,
+                       uint32_t box_cols, uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(DPK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    if (box_cols != 64) return fail(DPK_ERR_INVALID, "128-byte swizzle needs a 64-element box row");
+    if (!aligned16(base) || (row_stride_elems * 2) % 16 != 0 || (batch_stride_elems * 2) % 16 != 0)
+        return fail(DPK_ERR_INVALID, "tensor base, row stride and batch stride must be 16-byte aligned");
+    if (box_rows == 0 || box_rows > 256)
+        return fail(DPK_ERR_INVALID, "tensor-map box %ux%u out of range", box_cols, box_rows);
+    if (batches == 0) batches = 1;
+    if (batches == 1) batch_stride_elems = rows * row_stride_elems;    // unused, but must be valid
+    cuuint64_t dims[3] = {cols, rows, batches};
+    cuuint64_t strides[2] = {row_stride_elems * 2, batch_stride_elems * 2};
+    cuuint32_t box[3] = {box_cols, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(DPK_ERR_CUDA,
+                    "cuTensorMapEncodeTiled (3-D) failed with code %d (cols=%llu rows=%llu batches=%llu)",
+                    (int)r, (unsigned long long)cols, (unsigned long long)rows,
+                    (unsigned long long)batches);
+    return DPK_OK;
+}
+
 int make_tmap_2d_sw128(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
                        uint64_t row_stride_elems, uint32_t box_cols, uint32_t box_rows)
 {

@@ -34,6 +34,13 @@ int fail(int code, const char* fmt, ...);
 int make_tmap_2d_sw128(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
                        uint64_t row_stride_elems, uint32_t box_cols, uint32_t box_rows);
 
+// Batched form: `batches` such 2-D tensors `batch_stride_elems` apart, as a 3-D map whose box is
+// `box_cols` x `box_rows` x 1, so that rows past the end of one batch entry are zero-filled
+// instead of running into the next entry (or into unused capacity of a cache).
+int make_tmap_3d_sw128(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
+                       uint64_t batches, uint64_t row_stride_elems, uint64_t batch_stride_elems,
+                       uint32_t box_cols, uint32_t box_rows);
+
 // Same, without swizzle (rows of the box stored back to back).
 int make_tmap_2d_plain(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows,
                        uint64_t row_stride_elems, uint32_t box_cols, uint32_t box_rows);

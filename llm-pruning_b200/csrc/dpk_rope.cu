@@ -26,6 +26,7 @@ struct RopeParams {
     uint8_t* v_cache;
     int64_t cs_batch_stride; // elements between batches of cos/sin (0: shared)
     int64_t capacity, past_len;
+    int64_t q_ts, kv_ts;     // elements between consecutive tokens of q / of k and v
     int B, T, Hq, Hk, D;
 };
 
@@ -73,7 +74,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeParams p)
             // value head: plain copy into the cache
             if (!p.v_cache) continue;
             const int hv = head - p.Hq - p.Hk;
-            const uint8_t* src = p.v + ((tok * p.Hk + hv) * p.D) * 2;
+            const uint8_t* src = p.v + (tok * p.kv_ts + int64_t(hv) * p.D) * 2;
             uint8_t* dst = p.v_cache + (((int64_t(b) * p.capacity + p.past_len + t) * p.Hk + hv) * p.D) * 2;
             *reinterpret_cast<uint4*>(dst + lo_off) = *reinterpret_cast<const uint4*>(src + lo_off);
             *reinterpret_cast<uint4*>(dst + hi_off) = *reinterpret_cast<const uint4*>(src + hi_off);
@@ -87,10 +88,10 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeParams p)
         const uint4 s_hi = __ldg(reinterpret_cast<const uint4*>(sn + hi_off));
         uint8_t *src, *dst;
         if (head < p.Hq) {
-            src = dst = p.q + ((tok * p.Hq + head) * p.D) * 2;
+            src = dst = p.q + (tok * p.q_ts + int64_t(head) * p.D) * 2;
         } else {
             const int hk = head - p.Hq;
-            src = p.k + ((tok * p.Hk + hk) * p.D) * 2;
+            src = p.k + (tok * p.kv_ts + int64_t(hk) * p.D) * 2;
             dst = p.k_cache ? p.k_cache + (((int64_t(b) * p.capacity + p.past_len + t) * p.Hk + hk) * p.D) * 2
                             : src;
         }
@@ -110,7 +111,7 @@ using namespace dpk;
 extern "C" int dpk_rope_append(void* q, void* k, const void* v, const void* cos, const void* sin,
                                int64_t cs_batch_stride, void* k_cache, void* v_cache, int B, int T,
                                int Hq, int Hk, int D, int64_t capacity, int64_t past_len, int dtype,
-                               void* stream)
+                               int64_t q_token_stride, int64_t kv_token_stride, void* stream)
 {
     DPK_REQUIRE(q && k && cos && sin, "NULL tensor");
     DPK_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), "k_cache and v_cache go together");
@@ -126,6 +127,10 @@ extern "C" int dpk_rope_append(void* q, void* k, const void* v, const void* cos,
                     (long long)past_len);
     DPK_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(cos) && aligned16(sin) &&
                     aligned16(k_cache) && aligned16(v_cache), "tensors must be 16-byte aligned");
+    const int64_t q_ts = q_token_stride ? q_token_stride : int64_t(Hq) * D;
+    const int64_t kv_ts = kv_token_stride ? kv_token_stride : int64_t(Hk) * D;
+    DPK_REQUIRE(q_ts >= int64_t(Hq) * D && kv_ts >= int64_t(Hk) * D && q_ts % 8 == 0 && kv_ts % 8 == 0,
+                "token strides must cover a token's heads and be multiples of 8 elements");
     if (B == 0 || T == 0) return DPK_OK;
     RopeParams p;
     p.q = static_cast<uint8_t*>(q);
@@ -138,6 +143,8 @@ extern "C" int dpk_rope_append(void* q, void* k, const void* v, const void* cos,
     p.cs_batch_stride = cs_batch_stride;
     p.capacity = capacity;
     p.past_len = past_len;
+    p.q_ts = q_ts;
+    p.kv_ts = kv_ts;
     p.B = B;
     p.T = T;
     p.Hq = Hq;

@@ -43,17 +43,17 @@ SIGNATURES = {
     "dpk_ffn_swiglu": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp, _sz,
                               _vp]),
     "dpk_attn_prefill": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32,
-                                _i32, _i32, _f32, _i32, _i32, _i32, _vp]),
+                                _i32, _i32, _f32, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _vp]),
     "dpk_attn_decode_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32, _i32, _i32]),
     "dpk_attn_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32,
-                               _f32, _i32, _vp, _sz, _vp]),
+                               _f32, _i32, _i64, _i64, _vp, _sz, _vp]),
     "dpk_ffn_small_workspace_bytes": (_sz, [_i64, _i32, _i32]),
     "dpk_ffn_swiglu_small": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp,
                                     _sz, _vp]),
     "dpk_router_norm": (_i32, [_vp, _i64, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64,
                                _i32, _i32, _i32, _i32, _i32, _vp]),
     "dpk_rope_append": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _i32,
-                               _i64, _i64, _i32, _vp]),
+                               _i64, _i64, _i32, _i64, _i64, _vp]),
     "dpk_peer_alloc": (_i32, [_sz, C.POINTER(_vp), _vp]),
     "dpk_peer_open": (_i32, [_vp, C.POINTER(_vp)]),
     "dpk_peer_close": (_i32, [_vp]),

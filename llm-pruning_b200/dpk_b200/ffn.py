@@ -89,6 +89,9 @@ class RoutedFFN:
         M = xf.shape[0]
         if M > self.max_tokens:
             raise ValueError(f"{M} tokens exceed the planned maximum {self.max_tokens}")
+        if out is not None and self.row_parallel is not None:
+            raise ValueError("out= cannot be given with a row-parallel sum: the summed result lives "
+                             "in the buffer the ranks share and is returned as a view of it")
         m8 = _mask_bytes(mask.reshape(M, self.NG))
         y = out.view(M, self.H) if out is not None else torch.empty(
             (M, self.H), dtype=xf.dtype, device=self.device)

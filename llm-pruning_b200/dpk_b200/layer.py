@@ -1,8 +1,10 @@
 """A pruned decoder layer assembled from the routed operators (inference).
 
-Attention block: routed Q projection (``gemm_mn`` over head groups), dense K/V
-projections, head-group-routed attention, routed output projection (``gemm_k``);
-then the dynamic-width SwiGLU FFN.  Both sub-blocks add their input back
+Attention block: Q, K and V projections in ONE routed ``gemm_mn`` launch over the stacked
+weight ``[Wq; Wk; Wv]`` (the query channels routed by head group, the K/V channels as groups
+that every token keeps), head-group-routed attention reading q, k, v as column slices of
+that launch's output, routed output projection (``gemm_k``); then the dynamic-width SwiGLU
+FFN.  Both sub-blocks add their input back
 (residual).  Under tensor parallelism each rank holds the weights of its KV-head
 groups and FFN channel groups (:mod:`dpk_b200.tp`) and the two row-parallel outputs
 are summed with one all-reduce each -- the FFN router of the reference reads the
@@ -27,6 +29,8 @@ from __future__ import annotations
 
 from typing import Optional
 
+import math
+
 import torch
 import torch.distributed as dist
 
@@ -42,13 +46,23 @@ class RoutedDecoderLayer:
         """All weights are this rank's slices: ``wq [Hq_l*D, H]``, ``wk/wv [Hk_l*D, H]``,
         ``wo [H, Hq_l*D]``, ``wg/wu [I_l, H]``, ``wd [H, I_l]``; the head and group counts
         are local too."""
-        self.wq, self.wk, self.wv, self.wo = (w.contiguous() for w in (wq, wk, wv, wo))
         self.Hq, self.Hk, self.D = num_q_heads, num_kv_heads, head_dim
         self.attn_groups = attn_groups
+        self.wo = wo.contiguous()
+        # one stacked weight; wq / wk / wv stay available as row slices of it
+        qd, kd = num_q_heads * head_dim, num_kv_heads * head_dim
+        self.wqkv = torch.cat([wq, wk, wv], dim=0).contiguous()
+        self.wq, self.wk, self.wv = self.wqkv[:qd], self.wqkv[qd:qd + kd], self.wqkv[qd + kd:]
+        # group width of the stacked launch: divides a head group's query channels and the K/V
+        # channels; 256 (one UMMA tile of output channels) where the shapes allow
+        self.qkv_group = math.gcd(math.gcd(qd // attn_groups, 2 * kd), 256)
+        self.fold_qkv = self.qkv_group >= 64
+        self._qkv_out = None
         self.ffn = RoutedFFN(wg, wu, wd, ffn_groups, max_tokens)
         self.pg = process_group
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
         self.timers = None          # optional dict of CUDA event pairs per phase
+        self.ffn_events = None      # optional dict: event pairs around the two FFN GEMM kernels
         self.token_chunks = 1       # > 1: pipelined forward (see the module docstring)
         self.sum_o = None           # dpk_b200.peer.RowParallelSum pair: see fuse_sums()
         self.H = wo.shape[0]
@@ -82,22 +96,22 @@ class RoutedDecoderLayer:
         attention; routed output projection, summed over the ranks, ``x1 = x + o``;
         ``execute_ffn = decide(router_ffn(x1))``, ``h2 = post_attention_layernorm(x1)`` (one
         kernel); routed FFN of ``h2``, summed over the ranks; ``x1 + y``.
-        ``return_masks``: also return this rank's two routing masks."""
+        ``return_masks``: also return the two routing masks -- this rank's columns, or with
+        ``return_masks="full"`` the decisions for all groups (every rank computes them)."""
         f = self.front
         B, T, H = x.shape
         self._mark("start")
         am, h, _ = ops.router_norm(x, *f["attn"], norm_weight=f["n1"], eps=f["eps"])
+        am_all = am
         if f["ar"] is not None:
             am = am[..., f["ar"][0]:f["ar"][1]]
         self._mark("route1")
-        q, meta = ops.gemm_mn(h, self.wq, am)
-        k = (h @ self.wk.T).view(B, T, self.Hk, self.D)
-        v = (h @ self.wv.T).view(B, T, self.Hk, self.D)
-        q = q.view(B, T, self.Hq, self.D)
+        q, k, v = self.project_qkv(h, am)
         ops.rope_append(q, k, None, cos, sin)
         self._mark("qkv")
-        meta_attn = meta if B == 1 else {}
-        attn, _ = ops.attention_prefill(q, k, v, am, **meta_attn)
+        attn, meta = ops.attention_prefill(q, k, v, am)
+        if B != 1:
+            meta = {}        # per-batch layout (attention) vs flattened layout (GEMMs)
         self._mark("attn")
         if self.sum_o is not None:
             x1 = self.sum_o.routed_gemm_k(attn.view(B, T, self.Hq * self.D), self.wo, am,
@@ -109,18 +123,46 @@ class RoutedDecoderLayer:
             x1 = x + o
         self._mark("oproj")
         fm, h2, _ = ops.router_norm(x1, *f["ffn"], norm_weight=f["n2"], eps=f["eps"])
+        fm_all = fm
         if f["fr"] is not None:
             fm = fm[..., f["fr"][0]:f["fr"][1]]
         self._mark("route2")
         if self.ffn.row_parallel is not None:
-            out = self.ffn(h2, fm, residual=x1)
+            out = self.ffn(h2, fm, residual=x1, events=self.ffn_events)
         else:
-            y = self.ffn(h2, fm)
+            y = self.ffn(h2, fm, events=self.ffn_events)
             if self.world > 1:
                 dist.all_reduce(y, group=self.pg)
             out = x1 + y
         self._mark("ffn")
+        if return_masks == "full":
+            return out, am_all, fm_all
         return (out, am, fm) if return_masks else out
+
+    def project_qkv(self, h: torch.Tensor, attn_mask: torch.Tensor):
+        """``q [B,T,Hq,D]``, ``k, v [B,T,Hk,D]`` of ``h [B,T,H]``; rows of q whose head group is
+        routed out are left unwritten (attention never reads them)."""
+        B, T, _ = h.shape
+        qd, kd = self.Hq * self.D, self.Hk * self.D
+        if not self.fold_qkv:
+            q, _ = ops.gemm_mn(h, self.wq, attn_mask)
+            return (q.view(B, T, self.Hq, self.D), (h @ self.wk.T).view(B, T, self.Hk, self.D),
+                    (h @ self.wv.T).view(B, T, self.Hk, self.D))
+        G = self.qkv_group
+        per_head_group = qd // self.attn_groups // G
+        m = attn_mask.reshape(B, T, self.attn_groups)
+        m = m if m.dtype == torch.bool else m != 0
+        stacked = torch.cat([m.repeat_interleave(per_head_group, dim=-1),
+                             torch.ones((B, T, 2 * kd // G), dtype=torch.bool, device=h.device)], dim=-1)
+        width = qd + 2 * kd
+        if self._qkv_out is None or self._qkv_out.numel() < B * T * width or self._qkv_out.dtype != h.dtype:
+            self._qkv_out = torch.empty(B * T * width, dtype=h.dtype, device=h.device)
+        out = self._qkv_out[:B * T * width].view(B * T, width)
+        ops.gemm_mn(h, self.wqkv, stacked, D=out)
+        out = out.view(B, T, width)
+        return (out[..., :qd].view(B, T, self.Hq, self.D),
+                out[..., qd:qd + kd].view(B, T, self.Hk, self.D),
+                out[..., qd + kd:].view(B, T, self.Hk, self.D))
 
     def _mark(self, name):
         if self.timers is not None:
@@ -133,14 +175,16 @@ class RoutedDecoderLayer:
         [B,T,ffn_groups]`` (this rank's columns).  Returns the layer output ``[B,T,H]``."""
         B, T, H = x.shape
         if self.token_chunks > 1 and B == 1 and T >= 256 * self.token_chunks:
+            if self.sum_o is not None or self.ffn.row_parallel is not None:
+                raise ValueError("token_chunks > 1 pipelines NCCL all-reduces; it cannot be combined "
+                                 "with fuse_sums() (the fused sums overlap by halves on their own)")
             return self._pipelined(x, attn_mask, ffn_mask)
         self._mark("start")
-        q, meta = ops.gemm_mn(x, self.wq, attn_mask)
-        k = (x @ self.wk.T).view(B, T, self.Hk, self.D)
-        v = (x @ self.wv.T).view(B, T, self.Hk, self.D)
+        q, k, v = self.project_qkv(x, attn_mask)
         self._mark("qkv")
-        meta_attn = meta if B == 1 else {}       # per-batch vs flattened layouts differ for B > 1
-        attn, _ = ops.attention_prefill(q.view(B, T, self.Hq, self.D), k, v, attn_mask, **meta_attn)
+        attn, meta = ops.attention_prefill(q, k, v, attn_mask)
+        if B != 1:
+            meta = {}        # per-batch layout (attention) vs flattened layout (GEMMs)
         self._mark("attn")
         if self.sum_o is not None:
             # x1 = x + sum over ranks of o; layer output = x1 + sum over ranks of y
@@ -169,10 +213,7 @@ class RoutedDecoderLayer:
         _, T, H = x.shape
         step = ((T + self.token_chunks - 1) // self.token_chunks + 127) // 128 * 128
         spans = [(s, min(s + step, T)) for s in range(0, T, step)]
-        q, meta = ops.gemm_mn(x, self.wq, attn_mask)
-        k = (x @ self.wk.T).view(1, T, self.Hk, self.D)
-        v = (x @ self.wv.T).view(1, T, self.Hk, self.D)
-        q = q.view(1, T, self.Hq, self.D)
+        q, k, v = self.project_qkv(x, attn_mask)
         nopad = torch.zeros(1, dtype=torch.int32, device=x.device)     # selects bottom-right alignment
         o = torch.empty_like(x)
         y = torch.empty_like(x)

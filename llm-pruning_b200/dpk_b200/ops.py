@@ -58,6 +58,22 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+def _heads_view(t: torch.Tensor) -> Tuple[torch.Tensor, int, int]:
+    """``t [B,T,heads,D]`` as the kernels address it: the heads of a token back to back, token
+    and batch strides free (multiples of 8 elements, 16-byte aligned base).  Returns
+    ``(tensor, token_stride, batch_stride)`` in elements, copying only a tensor that does not
+    fit -- a slice of a fused projection's output or the first rows of a KV cache with spare
+    capacity is read in place."""
+    B, T, Hh, D = t.shape
+    heads_packed = t.stride(3) == 1 and (Hh == 1 or t.stride(2) == D)
+    ts = t.stride(1) if T > 1 else Hh * D          # a stride over a dimension of one is never used
+    bs = t.stride(0) if B > 1 else T * ts
+    if not (heads_packed and ts >= Hh * D and ts % 8 == 0 and bs % 8 == 0 and t.data_ptr() % 16 == 0):
+        t = t.contiguous()
+        ts, bs = Hh * D, T * Hh * D
+    return t, ts, bs
+
+
 # --------------------------------------------------------------------------- routing
 
 def topk_route_mask(logits: torch.Tensor, keep: int) -> torch.Tensor:
@@ -128,8 +144,17 @@ def rope_append(q: torch.Tensor, k: torch.Tensor, v: Optional[torch.Tensor], cos
     Hk = k.shape[2]
     if k.shape != (B, T, Hk, D) or (v is not None and v.shape != k.shape):
         raise ValueError("q, k, v must be [B,T,heads,D] with equal B, T, D")
-    if not (q.is_contiguous() and k.is_contiguous() and (v is None or v.is_contiguous())):
-        raise ValueError("q, k, v must be contiguous (q and k are rotated in place)")
+    def flat_stride(t, heads):
+        # tokens of all batch entries one stride apart: [B*T, width] rows with the heads packed
+        ok = (t.stride(3) == 1 and (heads == 1 or t.stride(2) == D) and t.stride(1) % 8 == 0
+              and t.stride(1) >= heads * D and (B == 1 or t.stride(0) == T * t.stride(1)))
+        if not ok:
+            raise ValueError("q, k, v must keep a token's heads back to back and all tokens one stride "
+                             "apart (q and k are rotated in place, so no copy is made)")
+        return t.stride(1)
+    q_ts, kv_ts = flat_stride(q, Hq), flat_stride(k, Hk)
+    if v is not None and flat_stride(v, Hk) != kv_ts:
+        raise ValueError("k and v must share one token stride")
     if cos.dim() == 2:
         cos, sin = cos[None], sin[None]
     if cos.shape[-2:] != (T, D) or sin.shape != cos.shape or cos.shape[0] not in (1, B):
@@ -150,7 +175,7 @@ def rope_append(q: torch.Tensor, k: torch.Tensor, v: Optional[torch.Tensor], cos
     with torch.cuda.device(dev):
         N.check(N.load().dpk_rope_append(q.data_ptr(), k.data_ptr(), _ptr(v), cos.data_ptr(),
                                          sin.data_ptr(), stride, _ptr(k_cache), _ptr(v_cache), B, T,
-                                         Hq, Hk, D, capacity, past_len, code, _stream()))
+                                         Hq, Hk, D, capacity, past_len, code, q_ts, kv_ts, _stream()))
     if k_cache is None:
         return q, k, v
     return q, k_cache[:, :past_len + T], v_cache[:, :past_len + T]
@@ -427,7 +452,12 @@ def attention_prefill(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Mask: t
     B, Tq, Hq, D = Q.shape
     _, Tk, Hk, _ = K.shape
     NG = Mask.shape[-1]
-    Qc, Kc, Vc = Q.contiguous(), K.contiguous(), V.contiguous()
+    Qc, q_ts, q_bs = _heads_view(Q)
+    Kc, kv_ts, kv_bs = _heads_view(K)
+    Vc, v_ts, v_bs = _heads_view(V)
+    if (v_ts, v_bs) != (kv_ts, kv_bs):            # the kernel takes one pair of strides for K and V
+        Kc, Vc = K.contiguous(), V.contiguous()
+        kv_ts, kv_bs = Hk * D, Tk * Hk * D
     if O is None:
         O = torch.zeros((B, Tq, Hq, D), dtype=Q.dtype, device=dev)
     if not O.is_contiguous():
@@ -443,7 +473,8 @@ def attention_prefill(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Mask: t
         N.check(N.load().dpk_attn_prefill(Qc.data_ptr(), Kc.data_ptr(), Vc.data_ptr(),
                                           sidx.data_ptr(), counts.data_ptr(), _ptr(lp),
                                           O.data_ptr(), B, Tq, Tk, Hq, Hk, D, NG, float(scale),
-                                          1 if is_causal else 0, shift, code, _stream()))
+                                          1 if is_causal else 0, shift, code, q_ts, q_bs, kv_ts, kv_bs,
+                                          _stream()))
     return O, dict(sorted_mask=smask, sorted_indices=sidx)
 
 
@@ -470,7 +501,12 @@ def attention_decode(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Mask: to
     B, _, Hq, D = Q.shape
     _, Tk, Hk, _ = K.shape
     NG = Mask.shape[-1]
-    Qc, Kc, Vc = Q.contiguous(), K.contiguous(), V.contiguous()
+    Qc = Q.contiguous()
+    Kc, kv_ts, kv_bs = _heads_view(K)
+    Vc, v_ts, v_bs = _heads_view(V)
+    if (v_ts, v_bs) != (kv_ts, kv_bs):
+        Kc, Vc = K.contiguous(), V.contiguous()
+        kv_ts, kv_bs = Hk * D, Tk * Hk * D
     if O is None:
         O = torch.empty((B, 1, Hq, D), dtype=Q.dtype, device=dev)
     if not O.is_contiguous():
@@ -485,7 +521,7 @@ def attention_decode(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Mask: to
     with torch.cuda.device(dev):
         N.check(lib.dpk_attn_decode(Qc.data_ptr(), Kc.data_ptr(), Vc.data_ptr(), m8.data_ptr(),
                                     _ptr(lp), O.data_ptr(), B, Tk, Hq, Hk, D, NG, float(scale), code,
-                                    ws.data_ptr(), nbytes, _stream()))
+                                    kv_ts, kv_bs, ws.data_ptr(), nbytes, _stream()))
     return O, dict()
 
 

@@ -41,6 +41,8 @@ __all__ = [
     "attention_prefill",
     "attention_decode",
     "dense_then_mask_ffn",
+    "decoder_layer_rows",
+    "dense_then_mask_layer_rows",
     "rel_err",
     "rel_err_active",
     "rel_err_rows",
@@ -302,7 +304,8 @@ def dense_then_mask_ffn(x, Wg, Wu, Wd, mask):
 
 def attention(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, mask: torch.Tensor,
               scale: Optional[float] = None, leftpad: Optional[torch.Tensor] = None,
-              is_causal: bool = False, q_chunk: int = 1024) -> torch.Tensor:
+              is_causal: bool = False, q_chunk: int = 1024,
+              q_positions: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Query-head-group routed attention (``python/references.py:89-149``).
 
     ``Q,O: [B,Tq,Hq,D]``; ``K,V: [B,Tk,Hk,D]``; ``mask: [B,Tq,NG]``.  Group
@@ -313,6 +316,10 @@ def attention(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, mask: torch.Ten
     ``Leftpad`` is given, bottom-right (``k <= q + Tk - Tq``) when one is
     (``references.py:123-139``); the two agree when ``Tq == Tk``.  Keys
     ``k < leftpad[b]`` are excluded.
+
+    ``q_positions`` (int64 ``[Tq]``): the sequence position of each query row when ``Q`` holds
+    a sample of the rows of a longer sequence (rows of attention are independent, so a
+    full-size case can be checked on a sample); causal masking then uses these positions.
     """
     if Q.dim() != 4 or K.dim() != 4 or V.dim() != 4:
         raise ValueError("Q, K, and V must have shape [B, T, H, D]")
@@ -332,6 +339,12 @@ def attention(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, mask: torch.Ten
     out = torch.zeros((B, Tq, Hq, D), dtype=torch.float32)
     kpos = torch.arange(Tk)
     causal_shift = (Tk - Tq) if leftpad is not None else 0
+    if q_positions is not None:
+        if leftpad is not None or q_positions.shape != (Tq,):
+            raise ValueError("q_positions is a [Tq] vector and excludes Leftpad")
+        qpos = q_positions.to(torch.int64)
+    else:
+        qpos = torch.arange(Tq)
     for b in range(B):
         lp = int(leftpad[b]) if leftpad is not None else 0
         for h in range(Hq):
@@ -347,7 +360,7 @@ def attention(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, mask: torch.Ten
                 s = (q @ kh.T) * sc
                 allow = (kpos[None, :] >= lp)
                 if is_causal:
-                    allow = allow & (kpos[None, :] <= (r[:, None] + causal_shift))
+                    allow = allow & (kpos[None, :] <= (qpos[r][:, None] + causal_shift))
                 s = s.masked_fill(~allow, float("-inf"))
                 mx = s.max(dim=-1, keepdim=True).values
                 mx = torch.where(torch.isinf(mx), torch.zeros_like(mx), mx)
@@ -371,6 +384,97 @@ def attention_decode(Q, K, V, mask, **kw):
     """``python/references.py:166-175``: one query token, non-causal."""
     kw.setdefault("is_causal", False)
     return attention(Q, K, V, mask, **kw)
+
+
+# ----------------------------------------------------------------------------
+# the pruned decoder layer on a sample of its token rows
+# ----------------------------------------------------------------------------
+
+def decoder_layer_rows(x: torch.Tensor, rows: torch.Tensor, w: dict, attn_mask_rows: torch.Tensor,
+                       ffn_mask_rows: torch.Tensor, *, num_q_heads: int, num_kv_heads: int,
+                       head_dim: int, norm1: Optional[torch.Tensor] = None,
+                       norm2: Optional[torch.Tensor] = None, eps: float = 1e-5,
+                       cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+                       handoff: Optional[torch.dtype] = None, return_x1: bool = False):
+    """Output rows ``rows`` of the pruned decoder layer for one sequence ``x [1,T,H]``.
+
+    Data flow of ``WrapperDecoderLayer.forward`` (``WIDE/wrapper/attn_group_ffn_block.py:
+    148-218``) with the routing decisions given: ``h = input_layernorm(x)``; routed Q
+    projection, dense K/V projections, rotary embedding, head-group-routed causal
+    attention, routed output projection, ``x1 = x + o``; ``h2 = post_attention_layernorm(x1)``;
+    routed SwiGLU FFN; ``x1 + y``.  Every step after the K/V projections is independent per
+    token, so only the sampled rows are computed; K and V are computed for all tokens.
+
+    ``w``: fp32 ``wq [Hq*D,H]``, ``wk, wv [Hk*D,H]``, ``wo [H,Hq*D]``, ``wg, wu [I,H]``,
+    ``wd [H,I]``.  ``attn_mask_rows [1,R,NGa]`` / ``ffn_mask_rows [1,R,NGf]``: the decisions
+    for the sampled rows.  ``norm1/norm2`` ``None`` = no normalisation, ``cos/sin [T,D]``
+    ``None`` = no rotary embedding.  ``handoff`` (e.g. bf16) rounds every tensor that the GPU
+    path stores in that dtype between two kernels; ``None`` keeps fp32 throughout.
+    """
+    if x.dim() != 3 or x.shape[0] != 1:
+        raise ValueError("x must be [1,T,H]")
+    T, H = x.shape[1], x.shape[2]
+    Hq, Hk, D = num_q_heads, num_kv_heads, head_dim
+    rows = rows.to(torch.int64)
+    R = rows.numel()
+    rd = (lambda t: _round_to(t, handoff))
+    xf = x.to(torch.float32)
+    if norm1 is not None:
+        h = rms_norm(xf if handoff is None else xf.to(handoff), norm1, eps).to(torch.float32)
+    else:
+        h = xf
+    k = rd(h[0] @ w["wk"].T).view(1, T, Hk, D)
+    v = rd(h[0] @ w["wv"].T).view(1, T, Hk, D)
+    hr = h[:, rows]
+    q = rd(gemm_mn(hr, w["wq"], attn_mask_rows)).view(1, R, Hq, D)
+    if cos is not None:
+        c32, s32 = cos.to(torch.float32)[None], sin.to(torch.float32)[None]
+        k = rd(rope(k, c32, s32))
+        q = rd(rope(q, c32[:, rows], s32[:, rows]))
+    a = rd(attention(q, k, v, attn_mask_rows, is_causal=True, q_positions=rows)).view(1, R, Hq * D)
+    x1 = rd(xf[:, rows] + rd(gemm_k(a, w["wo"], attn_mask_rows)))
+    if norm2 is not None:
+        h2 = rms_norm(x1 if handoff is None else x1.to(handoff), norm2, eps).to(torch.float32)
+    else:
+        h2 = x1
+    y = ffn_swiglu(h2, w["wg"], w["wu"], w["wd"], ffn_mask_rows, round_intermediate=handoff)
+    out = x1 + y
+    return (out, x1) if return_x1 else out
+
+
+def dense_then_mask_layer_rows(x: torch.Tensor, rows: torch.Tensor, w: dict, k: torch.Tensor,
+                               v: torch.Tensor, attn_mask_rows: torch.Tensor,
+                               ffn_mask_rows: torch.Tensor, *, num_q_heads: int, num_kv_heads: int,
+                               head_dim: int) -> torch.Tensor:
+    """Cost model of the reference's CPU path for the same layer, on a sample of token rows:
+    every operator computes the dense product (or dense attention over all heads, SDPA as in
+    ``python/references.py:131-139``) and masks afterwards (``references.py:50-53, 83-85,
+    141-148``).  The K/V projections are computed for the sampled rows too -- and thrown away,
+    attention reads the given ``k, v [1,T,Hk,D]`` -- so that the timed work is exactly
+    ``R/T`` of the full layer's.  Used only as the timed CPU baseline."""
+    T, H = x.shape[1], x.shape[2]
+    Hq, Hk, D = num_q_heads, num_kv_heads, head_dim
+    rows = rows.to(torch.int64)
+    R = rows.numel()
+    xr = x[0, rows].to(torch.float32)
+    am = as_group_mask(attn_mask_rows, 1, R)[0]
+    NGa = am.shape[-1]
+    q = (xr @ w["wq"].T).view(R, NGa, -1).masked_fill(~am[..., None], 0).view(1, R, Hq, D)
+    _ = xr @ w["wk"].T, xr @ w["wv"].T
+    # dense attention over all heads in chunks of rows (bounds the score matrix); a chunk
+    # reads the keys up to its last row, as a causal kernel over the full sequence would
+    a = torch.empty(R, Hq, D)
+    order = torch.argsort(rows)
+    for c0 in range(0, R, 256):
+        sel = order[c0:c0 + 256]
+        kmax = int(rows[sel].max()) + 1
+        allow = torch.arange(kmax)[None, :] <= rows[sel][:, None]
+        a[sel] = torch.nn.functional.scaled_dot_product_attention(
+            q[:, sel].transpose(1, 2), k[:, :kmax].transpose(1, 2), v[:, :kmax].transpose(1, 2),
+            attn_mask=allow[None, None], enable_gqa=Hq != Hk).transpose(1, 2)[0]
+    a = a.reshape(R, NGa, -1).masked_fill(~am[..., None], 0).reshape(R, Hq * D)
+    x1 = xr + a @ w["wo"].T
+    return x1[None] + dense_then_mask_ffn(x1[None], w["wg"], w["wu"], w["wd"], ffn_mask_rows)
 
 
 # ----------------------------------------------------------------------------

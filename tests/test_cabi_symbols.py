@@ -58,7 +58,7 @@ def test_argument_checks_reject_before_any_launch(lib):
     rc = lib.dpk_gemm_k(p, 128, p, 128, p, p, p, 64, 8, 64, 128, 2, 7, None, 0, None)
     assert rc == N.ERR_INVALID
     # head_dim outside {64,128}
-    rc = lib.dpk_attn_prefill(p, p, p, p, p, None, p, 1, 16, 16, 4, 2, 96, 2, 0.1, 1, 0, N.BF16, None)
+    rc = lib.dpk_attn_prefill(p, p, p, p, p, None, p, 1, 16, 16, 4, 2, 96, 2, 0.1, 1, 0, N.BF16, 0, 0, 0, 0, None)
     assert rc == N.ERR_INVALID and "head_dim" in N.last_error()
     # keep outside [0, NG]
     rc = lib.dpk_topk_mask(p, 4, 8, 9, p, None)

@@ -6,6 +6,7 @@ import numpy as np
 import pytest
 import torch
 
+import conftest
 import golden_io
 from oracle import dpk_oracle as O
 from oracle import route_oracle as RO
@@ -34,9 +35,16 @@ def dev(t, dtype=None):
     return t.to(dtype) if dtype is not None else t
 
 
+def _test_label():
+    import os
+    return os.environ.get("PYTEST_CURRENT_TEST", "?").split(" ")[0].split("::")[-1]
+
+
 def assert_rel(actual, expected, tol=TOL):
     """Strict form: max|err| <= tol * rms(expected) over the whole output."""
     err = O.rel_err(actual.float().cpu(), expected)
+    if tol > TOL:
+        conftest.record_strict(_test_label(), err, f"strict form with a wider bound {tol}")
     assert err <= tol, f"max-abs error / rms = {err:.4g} > {tol}"
 
 
@@ -45,12 +53,14 @@ def assert_rel_active(actual, expected, tol=TOL):
     exact zeros on both sides and must stay so)."""
     a = actual.float().cpu().reshape(expected.shape)
     err = O.rel_err_active(a, expected)
+    conftest.record_strict(_test_label(), O.rel_err(a, expected), f"rms over non-zero entries <= {tol}")
     assert err <= tol, f"max-abs error / rms(active) = {err:.4g} > {tol}"
 
 
 def assert_rel_rows(actual, expected, tol=TOL):
     """Attention: every output row against its own RMS."""
     err = O.rel_err_rows(actual.float().cpu(), expected)
+    conftest.record_strict(_test_label(), O.rel_err(actual.float().cpu(), expected), f"per-row rms <= {tol}")
     assert err <= tol, f"max over rows of max-abs error / rms(row) = {err:.4g} > {tol}"
 
 
@@ -1039,3 +1049,52 @@ def test_simulator_mlp_kernel_convention(ops):
     on = grp.repeat_interleave(I // 4, dim=-1).float()
     # the projection is rounded to bf16 before the bias is added and the sum rounded again
     assert_rel_active(single, (O.gemm_mn(x, w_up, grp) + b_up * on), tol=3e-2)
+
+
+def test_attention_reads_strided_kv_in_place(ops):
+    """K and V as the first rows of a [B,capacity,Hk,D] cache (B > 1: not contiguous) and q, k, v
+    as column slices of one fused projection output are read where they lie: no copy, and
+    whatever sits in the cache's unused capacity (NaN here) never reaches the result."""
+    from dpk_b200.wide import SeqFirstKVCache
+
+    bf = torch.bfloat16
+    g = seeded(77)
+    B, T, Hq, Hk, D, cap = 3, 500, 8, 2, 128, 640
+    width = (Hq + 2 * Hk) * D
+    fused = bf16r(torch.randn(B, T, width, generator=g))
+    fd = dev(fused, bf)
+    q = fd[..., :Hq * D].view(B, T, Hq, D)
+    k = fd[..., Hq * D:(Hq + Hk) * D].view(B, T, Hk, D)
+    v = fd[..., (Hq + Hk) * D:].view(B, T, Hk, D)
+    for t in (q, k, v):
+        got, ts, bs = ops._heads_view(t)
+        assert got.data_ptr() == t.data_ptr() and ts == width and bs == T * width
+    mask = torch.rand(B, T, 2, generator=g) > 0.3
+    qc, kc, vc = (fused[..., a:b].reshape(B, T, -1, D) for a, b in
+                  ((0, Hq * D), (Hq * D, (Hq + Hk) * D), ((Hq + Hk) * D, width)))
+    out, _ = ops.attention_prefill(q, k, v, dev(mask))
+    assert_rel_rows(out, O.attention_prefill(qc, kc, vc, mask))
+
+    # through the cache: rotary embedding in place on the slices, append, then decode and a
+    # second prefill over the cached rows
+    ang = torch.arange(T).float()[:, None] / (10000.0 ** (torch.arange(0, D, 2).float() / D))[None, :]
+    cos, sin = bf16r(torch.cat([ang, ang], -1).cos()), bf16r(torch.cat([ang, ang], -1).sin())
+    cache = SeqFirstKVCache(B, cap, Hk, D, bf, "cuda")
+    cache.keys.fill_(float("nan"))
+    cache.values.fill_(float("nan"))
+    qr, keys, values = cache.rope_update(q, k, v, dev(cos, bf), dev(sin, bf))
+    assert qr.data_ptr() == q.data_ptr() and keys.data_ptr() == cache.keys.data_ptr()
+    assert not keys.is_contiguous()
+    got, ts, bs = ops._heads_view(keys)
+    assert got.data_ptr() == keys.data_ptr() and (ts, bs) == (Hk * D, cap * Hk * D)
+    want_q = bf16r(O.rope(qc, cos[None], sin[None]))
+    want_k = bf16r(O.rope(kc, cos[None], sin[None]))
+    assert torch.equal(keys.float().cpu(), want_k) and torch.equal(values.float().cpu(), vc)
+    out2, _ = ops.attention_prefill(qr, keys, values, dev(mask))
+    assert torch.isfinite(out2.float()).all()
+    assert_rel_rows(out2, O.attention_prefill(want_q, want_k, vc, mask))
+    qd = bf16r(torch.randn(B, 1, Hq, D, generator=g))
+    dm = torch.tensor([[[True, False]], [[True, True]], [[False, True]]])
+    out3, _ = ops.attention_decode(dev(qd, bf), keys, values, dev(dm))
+    assert torch.isfinite(out3.float()).all()
+    assert_rel_rows(out3, O.attention_decode(qd, want_k, vc, dm))

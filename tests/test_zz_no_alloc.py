@@ -60,7 +60,8 @@ def test_static_scratch_matches_regular_entry_point_twice_in_a_row():
         es, ei = torch.sort(mask, dim=dim, descending=True, stable=True)
         assert torch.equal(si.cpu(), ei) and torch.equal(ss.cpu().view(torch.bool), es)
 
-    # beyond the built-in capacity (256 row blocks x 512 groups = 131072 counters): refused
+    # beyond the built-in capacity of 65536 counters (this call would need 256 row blocks x
+    # 512 groups = 131072): refused
     # on the host with a clear message; nothing is launched, so small buffers suffice
     dummy = torch.zeros(64, dtype=torch.int64, device="cuda")
     rc = lib.dpk_route_compact_static(dummy.data_ptr(), 1, 65536, 512, dummy.data_ptr(),
