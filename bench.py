@@ -569,11 +569,20 @@ def main():
                 dist.destroy_process_group()
             raise SystemExit(f"{where}: a kernel reported status {int(t.item())} (this rank: {status})")
 
-    # ---- N > 1: the sums with NCCL first (comparison and cross-check), then fused -------
+    # ---- N > 1: the sums with NCCL first (cross-check), then fused ---------------------------
+    # The check runs the operators with GIVEN routing masks (top-k of seeded logits): with the
+    # layer's own routers a last-bit difference in the summed hidden state flips decisions that
+    # sit on the boundary, which would be a routing difference, not a difference of the sums.
     sum_check = None
     fused = False
     if world > 1:
-        out_nccl = layer.forward_full(x, cos, sin).clone()
+        (ga0, ga1), (gf0, gf1) = shape.shard(world, rank)
+        gm = torch.Generator(device=device).manual_seed(29)
+        am_chk = ops.topk_route_mask(torch.randn(1, T, shape.attn_groups, generator=gm, device=device),
+                                     shape.attn_keep)[..., ga0:ga1]
+        fm_chk = ops.topk_route_mask(torch.randn(1, T, shape.ffn_groups, generator=gm, device=device),
+                                     shape.ffn_keep)[..., gf0:gf1]
+        out_nccl = layer(x, am_chk, fm_chk).clone()
         if args.sum == "fused":
             try:
                 layer.fuse_sums(T)
@@ -583,19 +592,31 @@ def main():
                 if rank == 0:
                     print(f"bench: {exc}; summing the partial outputs with NCCL instead", file=sys.stderr)
         if fused:
-            out_fused = layer.forward_full(x, cos, sin)
+            out_fused = layer(x, am_chk, fm_chk)
             a, b = out_fused.float(), out_nccl.float()
-            rel = float((a - b).abs().max() / b.pow(2).mean().sqrt())
+            rms_b = b.pow(2).mean().sqrt()
+            rel = torch.stack([(a - b).abs().max() / rms_b, (a - b).pow(2).mean().sqrt() / rms_b])
             digest = out_fused.view(torch.int16).to(torch.int64).sum().reshape(1)
             digests = [torch.empty_like(digest) for _ in range(world)]
             dist.all_gather(digests, digest)
             same = all(int(d.item()) == int(digests[0].item()) for d in digests)
-            t = torch.tensor([rel], device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            sum_check = {"fused_vs_nccl_max_abs_over_rms": float(t.item()), "tol": TOL,
+            dist.all_reduce(rel, op=dist.ReduceOp.MAX)
+            rel_max, rel_rms = float(rel[0].item()), float(rel[1].item())
+            # NCCL adds bf16 partial sums in bf16 (every rank's partial is rounded, and so is every
+            # hop of the reduction), the fused sum adds in fp32 and rounds once: single entries
+            # differ by a few bf16 ulps of the largest values (the maximum below), but the RMS of
+            # the difference stays at rounding level.  One misplaced 128-token window out of 16384
+            # tokens would put it near 1e-1, so the RMS bound is the check; the precise check of
+            # the fused output is the "parity" record against the oracle.
+            bound = 5e-3
+            sum_check = {"fused_vs_nccl_rms_diff_over_rms": rel_rms, "bound": bound,
+                         "fused_vs_nccl_max_abs_over_rms": rel_max,
                          "identical_output_on_every_rank": bool(same),
-                         "ok": bool(float(t.item()) <= TOL and same)}
-        del out_nccl
+                         "ok": bool(rel_rms <= bound and same),
+                         "how": "the layer's operators with given top-k masks, NCCL all-reduces (bf16 arithmetic) "
+                                "against the fused row-parallel sums (fp32, one rounding)"}
+            del out_fused
+        del out_nccl, am_chk, fm_chk
         check_status("cross-check of the sums")
 
     def step():
@@ -816,7 +837,7 @@ def main():
         "e2e": e2e,
         "parity": parity,
         "gpu_launches": (ours_l * args.steps) if ours_l else None,
-        "launches_per_step": {"this_library": ours_l, "other (cuBLAS K/V projections, element-wise, NCCL)": other_l},
+        "launches_per_step": {"this_library": ours_l, "other (torch element-wise ops on masks and residuals, NCCL)": other_l},
     }
     if dense is not None:
         line["dense"] = dense

@@ -248,6 +248,16 @@ int dpk_attn_prefill(const void* Q, const void* K, const void* V, const int64_t*
                      int causal_shift, int dtype, int64_t q_token_stride, int64_t q_batch_stride,
                      int64_t kv_token_stride, int64_t kv_batch_stride, void* stream);
 
+/*
+ * Which prefill-attention kernel dpk_attn_prefill launches: 0 or 1 (default) = one query head
+ * per CTA; 2 = two query heads per CTA sharing one K/V stream wherever heads 2i and 2i+1 share
+ * their routing group and KV head (Hq/NG and Hq/Hk even), one head per CTA elsewhere.  Both give
+ * the same bits; the one-head kernel measured faster.  Process-wide, for measurements and tests;
+ * the reference selects kernel versions the same way through its kernel_version argument
+ * (python/attention_prefill/jit.py:223-239).
+ */
+int dpk_set_attn_prefill_heads(int heads);
+
 /* Bytes of scratch dpk_attn_decode needs. */
 size_t dpk_attn_decode_workspace_bytes(int B, int Tk, int Hq, int Hk, int D, int NG);
 

@@ -24,6 +24,7 @@
 #define DPK_KERNEL_ID 5   // thousands digit of the device status word
 #include "dpk_host.h"
 #include "dpk_sm100.cuh"
+#include "dpk_attn_tc.cuh"
 
 namespace dpk {
 
@@ -32,7 +33,12 @@ constexpr int kTcBM = 128;        // query rows per CTA
 #define DPK_ATTN_BN 64
 #endif
 constexpr int kTcBN = DPK_ATTN_BN;          // keys per tile
-constexpr int kTcSBuf = 128 / kTcBN;        // score buffers in TMEM and K/V stages in shared memory
+constexpr int kTcSBuf = 128 / kTcBN;        // score buffers in TMEM and V stages in shared memory
+#ifndef DPK_ATTN_KSTAGES
+#define DPK_ATTN_KSTAGES kTcSBuf
+#endif
+constexpr int kTcKSt = DPK_ATTN_KSTAGES;    // K stages in shared memory (at most 4)
+static_assert(kTcKSt >= 2 && kTcKSt <= 4, "K ring depth");
 static_assert(kTcBN == 64 || kTcBN == 32, "tile width");
 constexpr int kTcThreads = 192;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
@@ -51,82 +57,6 @@ struct PrefillTcParams {
     int* status;
 };
 
-// MN-major operand tile stored as [rows = K index][64 contiguous MN elements] blocks of
-// 128-byte rows under the 128-byte swizzle: 8-row groups 1024 bytes apart (stride byte
-// offset), 64-element MN blocks `mn_block_bytes` apart (leading byte offset).
-__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_block_bytes)
-{
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
-    d |= static_cast<uint64_t>((mn_block_bytes >> 4) & 0x3FFFu) << 16;
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;
-    d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
-    return d;
-}
-
-__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&v)[32])
-{
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-        :
-        : "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
-          "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]),
-          "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
-          "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
-          "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&v)[16])
-{
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        :
-        : "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
-          "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]),
-          "r"(v[14]), "r"(v[15])
-        : "memory");
-}
-// P of one tile: as many 32-bit columns as the tile has key pairs
-__device__ __forceinline__ void tmem_st_p(uint32_t taddr, const uint32_t (&v)[32]) { tmem_st_32x32b_x32(taddr, v); }
-__device__ __forceinline__ void tmem_st_p(uint32_t taddr, const uint32_t (&v)[16]) { tmem_st_32x32b_x16(taddr, v); }
-__device__ __forceinline__ void tmem_st_wait()
-{
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-
-// D[tmem] (+)= A[tmem] * B[smem]^T: A is read from tensor memory (lane = row, every 32-bit
-// column holds two consecutive K elements of a 16-bit type).
-__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
-                                            uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
-        "}\n" ::"r"(tmem_d),
-        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ float tc_exp2(float x)
-{
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-__device__ __forceinline__ float tc_max3(float a, float b, float c)
-{
-    float d;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
-
 template <int D>
 struct TcSmem {
     static constexpr int kQBytes = kTcBM * D * 2;
@@ -134,7 +64,7 @@ struct TcSmem {
     static constexpr int kVBytes = kTcBN * D * 2;      // one V stage
     static constexpr int kOffQ = 0;
     static constexpr int kOffK = kOffQ + kQBytes;
-    static constexpr int kOffV = kOffK + kTcSBuf * kKBytes;
+    static constexpr int kOffV = kOffK + kTcKSt * kKBytes;
     static constexpr int kOffBar = kOffV + kTcSBuf * kVBytes;
     static constexpr int kTotal = kOffBar + 30 * 8 + 16;   // base must be 1024-byte aligned
 };
@@ -204,10 +134,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 
     if (warp == 4 && lane == 0) {
         mbar_init(q_full, 128);
-        for (int s = 0; s < kTcSBuf; ++s) {
+        for (int s = 0; s < kTcKSt; ++s) {
             mbar_init(&k_full[s], 1);
-            mbar_init(&v_full[s], 1);
             mbar_init(&k_empty[s], 1);
+        }
+        for (int s = 0; s < kTcSBuf; ++s) {
+            mbar_init(&v_full[s], 1);
             mbar_init(&v_empty[s], 1);
             mbar_init(&s_full[s], 1);
             mbar_init(&p_full[s], 128);
@@ -404,22 +336,35 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         // =================== TMA producer: K and V tiles ====================================
         if (lane == 0) {
             const int col_base = kvh * D;
-            for (int j = 0; j < ntiles; ++j) {
-                const int s = j % kTcSBuf;
-                const uint32_t ph = ((j / kTcSBuf) & 1) ^ 1;
-                const int kv0 = kv_begin + j * kTcBN;
-                if (!mbar_wait(&k_empty[s], ph, abort_flag, p.status, DPK_DEV_TIMEOUT_EMPTY)) break;
-                mbar_arrive_expect_tx(&k_full[s], L::kKBytes);
+            // K runs kTcKSt-1 tiles ahead of V: a K tile is needed one softmax earlier than the V
+            // tile of the same keys, and its stage is released earlier too (by Q K^T, not by P V)
+            bool live = true;
+            auto load_k = [&](int j) {
+                const int ks = j % kTcKSt;
+                if (!mbar_wait(&k_empty[ks], ((j / kTcKSt) & 1) ^ 1, abort_flag, p.status,
+                               DPK_DEV_TIMEOUT_EMPTY)) {
+                    live = false;
+                    return;
+                }
+                mbar_arrive_expect_tx(&k_full[ks], L::kKBytes);
 #pragma unroll
                 for (int kb = 0; kb < KBQ; ++kb)
-                    tma_load_3d(sK + s * L::kKBytes + kb * (kTcBN * 128), &tmK, &k_full[s],
-                                col_base + kb * 64, kv0, b);
-                if (!mbar_wait(&v_empty[s], ph, abort_flag, p.status, DPK_DEV_TIMEOUT_EMPTY)) break;
+                    tma_load_3d(sK + ks * L::kKBytes + kb * (kTcBN * 128), &tmK, &k_full[ks],
+                                col_base + kb * 64, kv_begin + j * kTcBN, b);
+            };
+            for (int j = 0; live && j < kTcKSt - 1 && j < ntiles; ++j) load_k(j);
+            for (int j = 0; live && j < ntiles; ++j) {
+                if (j + kTcKSt - 1 < ntiles) load_k(j + kTcKSt - 1);
+                if (!live) break;
+                const int s = j % kTcSBuf;
+                if (!mbar_wait(&v_empty[s], ((j / kTcSBuf) & 1) ^ 1, abort_flag, p.status,
+                               DPK_DEV_TIMEOUT_EMPTY))
+                    break;
                 mbar_arrive_expect_tx(&v_full[s], L::kVBytes);
 #pragma unroll
                 for (int kb = 0; kb < KBQ; ++kb)
                     tma_load_3d(sV + s * L::kVBytes + kb * (kTcBN * 128), &tmV, &v_full[s],
-                                col_base + kb * 64, kv0, b);
+                                col_base + kb * 64, kv_begin + j * kTcBN, b);
             }
         }
     } else {
@@ -430,8 +375,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
             const uint32_t idesc_o = umma_idesc_f16(kBf16 ? 1 : 0, kTcBM, D) | (1u << 16);
             bool ok = mbar_wait(q_full, 0, abort_flag, p.status, DPK_DEV_TIMEOUT_FULL);
             auto issue_s = [&](int j) -> bool {
-                const int s = j % kTcSBuf;
-                if (!mbar_wait(&k_full[s], (j / kTcSBuf) & 1, abort_flag, p.status, DPK_DEV_TIMEOUT_FULL))
+                const int s = j % kTcSBuf, ks = j % kTcKSt;
+                if (!mbar_wait(&k_full[ks], (j / kTcKSt) & 1, abort_flag, p.status, DPK_DEV_TIMEOUT_FULL))
                     return false;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_s0 + s * kTcBN;
@@ -439,13 +384,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
                 for (int kb = 0; kb < KBQ; ++kb) {
                     const uint64_t adesc = umma_desc_k_sw128(smem_u32(sQ) + kb * (kTcBM * 128));
                     const uint64_t bdesc =
-                        umma_desc_k_sw128(smem_u32(sK) + s * L::kKBytes + kb * (kTcBN * 128));
+                        umma_desc_k_sw128(smem_u32(sK) + ks * L::kKBytes + kb * (kTcBN * 128));
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
                         umma_f16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc_s, (kb | k) != 0 ? 1u : 0u);
                 }
                 umma_commit(&s_full[s]);
-                umma_commit(&k_empty[s]);
+                umma_commit(&k_empty[ks]);
                 return true;
             };
             for (int j = 0; ok && j < kTcSBuf && j < ntiles; ++j) ok = issue_s(j);

@@ -44,6 +44,7 @@ SIGNATURES = {
                               _vp]),
     "dpk_attn_prefill": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32,
                                 _i32, _i32, _f32, _i32, _i32, _i32, _i64, _i64, _i64, _i64, _vp]),
+    "dpk_set_attn_prefill_heads": (_i32, [_i32]),
     "dpk_attn_decode_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32, _i32, _i32]),
     "dpk_attn_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32,
                                _f32, _i32, _i64, _i64, _vp, _sz, _vp]),

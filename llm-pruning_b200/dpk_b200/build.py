@@ -34,6 +34,7 @@ SOURCES = [
     "dpk_ffn.cu",
     "dpk_attn_prefill.cu",
     "dpk_attn_prefill_tc.cu",
+    "dpk_attn_prefill_tc2.cu",
     "dpk_attn_decode.cu",
     "dpk_peer.cu",
     "dpk_router_norm.cu",

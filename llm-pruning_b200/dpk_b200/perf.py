@@ -65,7 +65,7 @@ def topk_mask(shape, keep, gen):
 def run_prefill(args):
     B, T, Hq, Hk, D, NG, keep = 1, args.tokens or 8192, 32, 8, 128, 8, 4
     gen = torch.Generator(device="cuda").manual_seed(SEED)
-    bf = torch.bfloat16
+    bf = torch.float16 if getattr(args, "fp16", False) else torch.bfloat16
     q = torch.randn(B, T, Hq, D, generator=gen, device="cuda").to(bf)
     k = torch.randn(B, T, Hk, D, generator=gen, device="cuda").to(bf)
     v = torch.randn(B, T, Hk, D, generator=gen, device="cuda").to(bf)
@@ -282,8 +282,12 @@ def main(argv=None):
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--tokens", type=int, default=0, help="override the token / KV length")
     ap.add_argument("--batch", type=int, default=0, help="override the decode batch")
+    ap.add_argument("--fp16", action="store_true", help="attention_prefill: fp16 tensors instead of bf16")
+    ap.add_argument("--heads-per-cta", type=int, default=0, choices=[0, 1, 2],
+                    help="attention_prefill: 2 = the two-heads-per-CTA kernel, 0/1 = one head per CTA")
     args = ap.parse_args(argv)
     assert torch.cuda.is_available(), "dpk_b200.perf needs a CUDA device"
+    _native.check(_native.load().dpk_set_attn_prefill_heads(args.heads_per_cta))
     if args.kernel == "attention_prefill":
         res = run_prefill(args)
     elif args.kernel == "attention_decode":

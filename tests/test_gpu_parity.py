@@ -1098,3 +1098,31 @@ def test_attention_reads_strided_kv_in_place(ops):
     out3, _ = ops.attention_decode(dev(qd, bf), keys, values, dev(dm))
     assert torch.isfinite(out3.float()).all()
     assert_rel_rows(out3, O.attention_decode(qd, want_k, vc, dm))
+
+
+@pytest.mark.parametrize("B,T,Hq,Hk,D,NG,causal", [(1, 1000, 8, 2, 128, 2, True), (2, 333, 8, 4, 64, 4, True),
+                                                     (1, 700, 4, 2, 128, 1, False), (1, 130, 16, 2, 128, 2, True)])
+def test_prefill_one_and_two_heads_per_cta(ops, B, T, Hq, Hk, D, NG, causal):
+    """Both prefill kernels on the same inputs: one query head per CTA (the default) and two
+    query heads per CTA sharing one K/V stream; each against the oracle, and against each other
+    (same arithmetic per head, so the bits agree)."""
+    from dpk_b200 import _native
+
+    bf = torch.bfloat16
+    g = seeded(91)
+    q, k, v = (bf16r(torch.randn(B, T, h, D, generator=g)) for h in (Hq, Hk, Hk))
+    mask = torch.rand(B, T, NG, generator=g) > 0.4
+    mask[:, -1] = True
+    want = O.attention(q, k, v, mask, is_causal=causal)
+    lib = _native.load()
+    outs = []
+    try:
+        for heads in (1, 2):
+            _native.check(lib.dpk_set_attn_prefill_heads(heads))
+            out, _ = ops.attention_prefill(dev(q, bf), dev(k, bf), dev(v, bf), dev(mask), is_causal=causal)
+            assert_rel_rows(out, want)
+            assert_ref_tol(out, want)
+            outs.append(out)
+    finally:
+        _native.check(lib.dpk_set_attn_prefill_heads(0))
+    assert torch.equal(outs[0], outs[1])
