@@ -61,6 +61,22 @@ def measured_peaks():
     return 1400.0, 1590.0, 6650.0, "fallback"
 
 
+def recorded_traffic(shape, world: int):
+    """DRAM bytes of one full-size launch of the dominant kernel as ncu measured them (read +
+    write), from the summary under profiles/; None for any other shape or split."""
+    if world != 1 or shape.tokens != 16384:
+        return None
+    path = os.path.join(ROOT, "profiles", "gemm_mn_pair_config5_counters.md")
+    try:
+        with open(path) as f:
+            for line in f:
+                if line.startswith("traffic_bytes_per_launch_config5_16384_tokens:"):
+                    return float(line.split(":", 1)[1])
+    except OSError:
+        pass
+    return None
+
+
 def make_config(shape, world: int, args) -> dict:
     """The ``config`` object of the JSON line; the same for both arms at a given N."""
     if world == 1:
@@ -806,8 +822,10 @@ def main():
                 "achieved": ach, "peak": sus, "unit": "TFLOP/s", "frac": ach / sus,
                 "peak_source": f"{peak_src} sustained bf16: the kernel is timed inside a seconds-long loop "
                                "of layer steps (see clocks)",
-                "frac_of_burst_peak": ach / burst, "traffic": None,
-                "traffic_note": "per-launch DRAM bytes of this kernel are in profiles/ (ncu), not measured by this run",
+                "frac_of_burst_peak": ach / burst, "traffic": recorded_traffic(shape, world),
+                "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape "
+                                  "under ncu, read from profiles/gemm_mn_pair_config5_counters.md (not "
+                                  "measured by this run; null for other shapes)",
                 "algorithmic_flops_per_launch": flops_mn, "launch_ms": k_mn}
     cpu = None
     if not args.no_cpu_baseline and world == 1:

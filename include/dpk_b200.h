@@ -181,12 +181,17 @@ int dpk_gemm_mn(const void* A, int64_t lda, const void* W, const void* W2, int64
  * D is overwritten (the behaviour of the reference's PyTorch path,
  * python/references.py:21-26, 83-86), accumulated in fp32 without atomics.
  *   A [M,K] lda, W [N,K] ldw, D [M,N] ldd; row_bits / win_bits from dpk_mask_pack;
+ *   residual: optional [M,N] ldr (NULL = none) added in fp32 before the single rounding --
+ *   D = residual + projection, the sub-block's skip connection in the same pass; it may be D
+ *   itself, which is the accumulate-onto-D behaviour of the reference's CuTe path
+ *   (python/gemm_k/jit.py:368);
  *   workspace: see dpk_gemm_k_workspace_bytes (may be NULL).
  * Requirements: G = K/NG a multiple of 64, N % 8 == 0, 16-byte aligned rows.
  */
 int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw, const uint32_t* row_bits,
                const uint32_t* win_bits, void* D, int64_t ldd, int64_t M, int N, int K, int NG,
-               int dtype, void* workspace, size_t workspace_bytes, void* stream);
+               int dtype, const void* residual, int64_t ldr, void* workspace, size_t workspace_bytes,
+               void* stream);
 
 /*
  * Optional scratch of dpk_gemm_k: with very few token windows (decode, M <= 512) the

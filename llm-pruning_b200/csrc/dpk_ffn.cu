@@ -68,7 +68,7 @@ int dpk_ffn_swiglu(const void* x, const void* Wg, const void* Wu, const void* Wd
     rc = dpk_gemm_mn(x, H, Wg, Wu, H, sidx, counts, h, I, M, I, H, NG, dtype, DPK_ACT_IDENTITY,
                      stream);
     if (rc) return rc;
-    return dpk_gemm_k(h, I, Wd, I, row_bits, win_bits, y, H, M, H, I, NG, dtype, ws + L.acc,
+    return dpk_gemm_k(h, I, Wd, I, row_bits, win_bits, y, H, M, H, I, NG, dtype, nullptr, 0, ws + L.acc,
                       up256(dpk_gemm_k_workspace_bytes(M, H)), stream);
 }
 

@@ -106,12 +106,15 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             const bool valid = r < p.M;
             const int n0 = nchunk * BN;
             uint8_t* out = p.D + (r * p.ldd + n0) * 2;
+            // residual row of this thread (with split accumulation the conversion pass adds it)
+            const uint8_t* res = (p.R && p.acc32 == nullptr) ? p.R + (r * p.ldr + n0) * 2 : nullptr;
             if (!window_any(mwin, split)) {
                 // no group (of this split) is active for any token of the window: the rows
-                // are zero; with split accumulation there is nothing to add
+                // are zero (plus the residual); with split accumulation there is nothing to add
                 if (valid && p.acc32 == nullptr)
                     for (int c = 0; c < BN && n0 + c < p.N; c += 8)
-                        *reinterpret_cast<uint4*>(out + c * 2) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(out + c * 2) =
+                            res ? *reinterpret_cast<const uint4*>(res + c * 2) : make_uint4(0, 0, 0, 0);
                 continue;
             }
             const int ab = acc_it & 1;
@@ -141,15 +144,9 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                 } else if (valid) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        if (q * 8 < n && n0 + c + q * 8 < p.N) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                w[j] = pack_half2<kBf16>(__uint_as_float(v[q * 8 + 2 * j]),
-                                                         __uint_as_float(v[q * 8 + 2 * j + 1]));
+                        if (q * 8 < n && n0 + c + q * 8 < p.N)
                             *reinterpret_cast<uint4*>(out + (c + q * 8) * 2) =
-                                make_uint4(w[0], w[1], w[2], w[3]);
-                        }
+                                pack8_plus_residual<kBf16>(v + q * 8, res ? res + (c + q * 8) * 2 : nullptr);
                     }
                 }
             }
@@ -305,14 +302,21 @@ gemm_k_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 
 // fp32 partial sums -> half output (after a split-K launch)
 template <bool kBf16>
-__global__ void gemm_k_convert_kernel(const float* __restrict__ acc, uint8_t* __restrict__ D,
-                                      int64_t ldd, int64_t M, int N)
+__global__ void gemm_k_convert_kernel(const float* __restrict__ acc, uint8_t* D, int64_t ldd,
+                                      const uint8_t* R, int64_t ldr, int64_t M, int N)
 {
     const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 2;
     if (i >= M * N) return;
     const int64_t r = i / N;
     const int n = static_cast<int>(i - r * N);      // N is even: the pair stays in one row
-    *reinterpret_cast<uint32_t*>(D + (r * ldd + n) * 2) = pack_half2<kBf16>(acc[i], acc[i + 1]);
+    float lo = acc[i], hi = acc[i + 1];
+    if (R) {
+        float rl, rh;
+        unpack_half2<kBf16>(*reinterpret_cast<const uint32_t*>(R + (r * ldr + n) * 2), rl, rh);
+        lo += rl;
+        hi += rh;
+    }
+    *reinterpret_cast<uint32_t*>(D + (r * ldd + n) * 2) = pack_half2<kBf16>(lo, hi);
 }
 
 }  // namespace dpk
@@ -354,8 +358,11 @@ __global__ void peer_push_rows_kernel(const uint8_t* __restrict__ src, KParams p
 static int gemm_k_run(const void* A, int64_t lda, const void* W, int64_t ldw,
                       const uint32_t* row_bits, const uint32_t* win_bits, void* D, int64_t ldd,
                       int64_t M, int N, int K, int NG, int dtype, void* workspace,
-                      size_t workspace_bytes, void* stream, const PeerOut* peer)
+                      size_t workspace_bytes, void* stream, const PeerOut* peer,
+                      const void* residual = nullptr, int64_t ldr = 0)
 {
+    DPK_REQUIRE(!residual || (!peer && ldr >= N && ldr % 8 == 0 && aligned16(residual)),
+                "residual: [M, ldr] with ldr >= N, a multiple of 8, 16-byte aligned, plain output only");
     DPK_REQUIRE(A && W && (D || peer) && row_bits && win_bits, "NULL tensor");
     DPK_REQUIRE(dtype == DPK_F16 || dtype == DPK_BF16, "dtype must be DPK_F16 or DPK_BF16");
     DPK_REQUIRE(M >= 0 && M < (1ll << 31) && N > 0 && K > 0 && NG > 0, "bad shape");
@@ -428,6 +435,8 @@ static int gemm_k_run(const void* A, int64_t lda, const void* W, int64_t ldw,
 
     KParams p;
     p.D = static_cast<uint8_t*>(D);
+    p.R = static_cast<const uint8_t*>(residual);
+    p.ldr = ldr;
     p.row_bits = row_bits;
     p.win_bits = win_bits;
     p.ldd = ldd;
@@ -482,9 +491,9 @@ static int gemm_k_run(const void* A, int64_t lda, const void* W, int64_t ldw,
         const unsigned blocks = static_cast<unsigned>((pairs + 255) / 256);
         uint8_t* d = static_cast<uint8_t*>(D);
         if (dtype == DPK_BF16)
-            gemm_k_convert_kernel<true><<<blocks, 256, 0, s>>>(p.acc32, d, ldd, M, N);
+            gemm_k_convert_kernel<true><<<blocks, 256, 0, s>>>(p.acc32, d, ldd, p.R, p.ldr, M, N);
         else
-            gemm_k_convert_kernel<false><<<blocks, 256, 0, s>>>(p.acc32, d, ldd, M, N);
+            gemm_k_convert_kernel<false><<<blocks, 256, 0, s>>>(p.acc32, d, ldd, p.R, p.ldr, M, N);
     }
     DPK_CUDA(cudaGetLastError());
     return DPK_OK;
@@ -494,12 +503,12 @@ static int gemm_k_run(const void* A, int64_t lda, const void* W, int64_t ldw,
 
 extern "C" int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw,
                           const uint32_t* row_bits, const uint32_t* win_bits, void* D, int64_t ldd,
-                          int64_t M, int N, int K, int NG, int dtype, void* workspace,
-                          size_t workspace_bytes, void* stream)
+                          int64_t M, int N, int K, int NG, int dtype, const void* residual,
+                          int64_t ldr, void* workspace, size_t workspace_bytes, void* stream)
 {
     DPK_REQUIRE(D != nullptr, "NULL tensor");
     return dpk::gemm_k_run(A, lda, W, ldw, row_bits, win_bits, D, ldd, M, N, K, NG, dtype, workspace,
-                           workspace_bytes, stream, nullptr);
+                           workspace_bytes, stream, nullptr, residual, ldr);
 }
 
 extern "C" size_t dpk_gemm_k_scatter_workspace_bytes(int64_t M, int N, int64_t ldd)

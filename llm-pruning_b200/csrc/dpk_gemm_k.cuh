@@ -17,6 +17,8 @@ constexpr int kMaxPeers = 8;
 
 struct KParams {
     uint8_t* D;              // [M, ldd] half
+    const uint8_t* R;        // optional [M, ldr] half added to the result before the one rounding
+    int64_t ldr;             // (the residual of a transformer sub-block); may alias D
     const uint32_t* row_bits;   // [M, words]
     const uint32_t* win_bits;   // [nwin, words]
     int64_t ldd;
@@ -39,6 +41,28 @@ struct KParams {
     int64_t rows_per_owner;
     uint8_t* peer[kMaxPeers];
 };
+
+// Eight consecutive outputs of a row: accumulator values (+ residual), rounded once.
+template <bool kBf16>
+__device__ __forceinline__ uint4 pack8_plus_residual(const uint32_t* v, const uint8_t* res)
+{
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]);
+    if (res) {
+        const uint4 r4 = *reinterpret_cast<const uint4*>(res);
+        const uint32_t rw[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float lo, hi;
+            unpack_half2<kBf16>(rw[j], lo, hi);
+            f[2 * j] += lo;
+            f[2 * j + 1] += hi;
+        }
+    }
+    return make_uint4(pack_half2<kBf16>(f[0], f[1]), pack_half2<kBf16>(f[2], f[3]),
+                      pack_half2<kBf16>(f[4], f[5]), pack_half2<kBf16>(f[6], f[7]));
+}
 
 constexpr size_t kKSmemBytes = 1024 + size_t(kRingBytes) +
                                (3 * kMaxStages + 4) * sizeof(uint64_t) + 16;

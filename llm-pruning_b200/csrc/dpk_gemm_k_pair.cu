@@ -133,6 +133,10 @@ gemm_k_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             } else {
                 out = p.D + (r * p.ldd + n0) * 2;
             }
+            const uint8_t* res = nullptr;     // this thread's residual row (plain output only)
+            if constexpr (!kPeer) {
+                if (p.R) res = p.R + (r * p.ldr + n0) * 2;
+            }
             if (!pair_any(pw)) {
                 if constexpr (kPeer) {
                     // the owner sums every slab: an unused window still contributes zeros
@@ -142,7 +146,8 @@ gemm_k_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                                 make_uint4(0, 0, 0, 0);
                 } else if (valid) {
                     for (int c = 0; c < 256 && n0 + c < p.N; c += 8)
-                        *reinterpret_cast<uint4*>(out + c * 2) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(out + c * 2) =
+                            res ? *reinterpret_cast<const uint4*>(res + c * 2) : make_uint4(0, 0, 0, 0);
                 }
                 continue;
             }
@@ -193,15 +198,9 @@ gemm_k_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 if (valid) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        if (n0 + c + q * 8 < p.N) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                w[j] = pack_half2<kBf16>(__uint_as_float(v[q * 8 + 2 * j]),
-                                                         __uint_as_float(v[q * 8 + 2 * j + 1]));
+                        if (n0 + c + q * 8 < p.N)
                             *reinterpret_cast<uint4*>(out + (c + q * 8) * 2) =
-                                make_uint4(w[0], w[1], w[2], w[3]);
-                        }
+                                pack8_plus_residual<kBf16>(v + q * 8, res ? res + (c + q * 8) * 2 : nullptr);
                     }
                 }
             }

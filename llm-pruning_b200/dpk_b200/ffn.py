@@ -79,8 +79,11 @@ class RoutedFFN:
         tensor-parallel caller uses to start the all-reduce of a finished chunk while the
         next one is being computed.
 
+        ``residual [..., H]``: added to the result in the down projection's epilogue (fp32, one
+        rounding): the skip connection of the sub-block without a pass of its own.
+
         With ``self.row_parallel`` set the down projection is the fused row-parallel sum
-        instead: the result (plus ``residual [..., H]`` when given) is the sum over the
+        instead: the result (plus ``residual`` when given) is the sum over the
         ranks, returned as a view of the shared output buffer."""
         lead = x.shape[:-1]
         xf = x.reshape(-1, self.H)
@@ -97,7 +100,7 @@ class RoutedFFN:
             (M, self.H), dtype=xf.dtype, device=self.device)
         lib, st, ck = self.lib, _stream(), N.check
         H, I, NG = self.H, self.I, self.NG
-        if 0 < M <= self.small_tokens and self.row_parallel is None and residual is None:
+        if 0 < M <= self.small_tokens and self.row_parallel is None and residual is None:    # decode-sized
             ev = None
             if events is not None:
                 ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
@@ -135,8 +138,11 @@ class RoutedFFN:
                 events.setdefault("gemm_mn", []).append((ev[0], ev[1]))
                 events.setdefault("gemm_k", []).append((ev[2], ev[3]))
             return ysum.view(*lead, H)
+        res2 = None
         if residual is not None:
-            raise ValueError("residual is only fused into the row-parallel sum")
+            res2 = residual.reshape(M, H)
+            if res2.stride(-1) != 1 or res2.stride(0) % 8 or res2.dtype != y.dtype:
+                raise ValueError("residual must be a [.., H] tensor of the output's dtype with 16-byte aligned rows")
         words = self.row_bits.shape[1]
         step = M if row_chunks <= 1 else max(128, ((M + row_chunks - 1) // row_chunks + 127) // 128 * 128)
         esz = y.element_size()
@@ -146,6 +152,8 @@ class RoutedFFN:
                               self.row_bits.data_ptr() + r0 * words * 4,
                               self.win_bits.data_ptr() + (r0 // 128) * words * 4,
                               y.data_ptr() + r0 * H * esz, H, rows, H, I, NG, self.code,
+                              res2.data_ptr() + r0 * res2.stride(0) * esz if res2 is not None else None,
+                              res2.stride(0) if res2 is not None else 0,
                               self.acc.data_ptr() if self.acc_bytes else None, self.acc_bytes, st))
             if chunk_done is not None:
                 chunk_done(y[r0:r0 + rows])

@@ -117,10 +117,12 @@ class RoutedDecoderLayer:
             x1 = self.sum_o.routed_gemm_k(attn.view(B, T, self.Hq * self.D), self.wo, am,
                                           residual=x.contiguous())
         else:
-            o, _ = ops.gemm_k(attn.view(B, T, self.Hq * self.D), self.wo, am, **meta)
             if self.world > 1:
+                o, _ = ops.gemm_k(attn.view(B, T, self.Hq * self.D), self.wo, am, **meta)
                 dist.all_reduce(o, group=self.pg)
-            x1 = x + o
+                x1 = x + o
+            else:       # the skip connection rides on the projection's epilogue
+                x1, _ = ops.gemm_k(attn.view(B, T, self.Hq * self.D), self.wo, am, residual=x, **meta)
         self._mark("oproj")
         fm, h2, _ = ops.router_norm(x1, *f["ffn"], norm_weight=f["n2"], eps=f["eps"])
         fm_all = fm
@@ -130,10 +132,12 @@ class RoutedDecoderLayer:
         if self.ffn.row_parallel is not None:
             out = self.ffn(h2, fm, residual=x1, events=self.ffn_events)
         else:
-            y = self.ffn(h2, fm, events=self.ffn_events)
             if self.world > 1:
+                y = self.ffn(h2, fm, events=self.ffn_events)
                 dist.all_reduce(y, group=self.pg)
-            out = x1 + y
+                out = x1 + y
+            else:
+                out = self.ffn(h2, fm, events=self.ffn_events, residual=x1)
         self._mark("ffn")
         if return_masks == "full":
             return out, am_all, fm_all
@@ -196,16 +200,22 @@ class RoutedDecoderLayer:
             self._mark("ffn")
             self._mark("ar2")
             return out
+        if self.world == 1:     # both skip connections ride on the projections' epilogues
+            x1, _ = ops.gemm_k(attn.view(B, T, self.Hq * self.D), self.wo, attn_mask, residual=x, **meta)
+            self._mark("oproj")
+            self._mark("ar1")
+            out = self.ffn(x1, ffn_mask, residual=x1)
+            self._mark("ffn")
+            self._mark("ar2")
+            return out
         o, _ = ops.gemm_k(attn.view(B, T, self.Hq * self.D), self.wo, attn_mask, **meta)
         self._mark("oproj")
-        if self.world > 1:
-            dist.all_reduce(o, group=self.pg)
+        dist.all_reduce(o, group=self.pg)
         self._mark("ar1")
         x1 = x + o
         y = self.ffn(x1, ffn_mask)
         self._mark("ffn")
-        if self.world > 1:
-            dist.all_reduce(y, group=self.pg)
+        dist.all_reduce(y, group=self.pg)
         self._mark("ar2")
         return x1 + y
 
@@ -219,19 +229,26 @@ class RoutedDecoderLayer:
         y = torch.empty_like(x)
         x1 = torch.empty_like(x)
         ar1, ar2 = [], []
+        if self.world == 1:
+            # nothing to reduce: the skip connections ride on the projections' epilogues,
+            # exactly as in the unchunked call
+            for s, e in spans:
+                am = attn_mask[:, s:e]
+                attn, meta_c = ops.attention_prefill(q[:, s:e], k[:, :e], v[:, :e], am, Leftpad=nopad)
+                ops.gemm_k(attn.view(1, e - s, self.Hq * self.D), self.wo, am, D=x1[:, s:e],
+                           residual=x[:, s:e], **meta_c)
+                self.ffn(x1[:, s:e], ffn_mask[:, s:e], out=y[:, s:e], residual=x1[:, s:e])
+            return y
         for s, e in spans:
             am = attn_mask[:, s:e]
             attn, meta_c = ops.attention_prefill(q[:, s:e], k[:, :e], v[:, :e], am, Leftpad=nopad)
             ops.gemm_k(attn.view(1, e - s, self.Hq * self.D), self.wo, am, D=o[:, s:e], **meta_c)
-            ar1.append(dist.all_reduce(o[:, s:e], group=self.pg, async_op=True)
-                       if self.world > 1 else None)
+            ar1.append(dist.all_reduce(o[:, s:e], group=self.pg, async_op=True))
         for (s, e), work in zip(spans, ar1):
-            if work is not None:
-                work.wait()                               # the compute stream waits, not the host
+            work.wait()                                   # the compute stream waits, not the host
             torch.add(x[:, s:e], o[:, s:e], out=x1[:, s:e])
             self.ffn(x1[:, s:e], ffn_mask[:, s:e], out=y[:, s:e])
-            if self.world > 1:
-                ar2.append(dist.all_reduce(y[:, s:e], group=self.pg, async_op=True))
+            ar2.append(dist.all_reduce(y[:, s:e], group=self.pg, async_op=True))
         for work in ar2:
             work.wait()
         return x1.add_(y)

@@ -322,10 +322,16 @@ def _use_gemv_k_dispatch(M: int, G: int) -> bool:
 def gemm_k(A: torch.Tensor, B: torch.Tensor, Mask: torch.Tensor, D: Optional[torch.Tensor] = None,
            sorted_mask: Optional[torch.Tensor] = None, sorted_indices: Optional[torch.Tensor] = None,
            estimate_sparsity: Optional[float] = 0.5, kernel_version: Optional[int] = 0,
-           arch: Optional[str] = "sm100", autotune: Optional[bool] = True, cudagraph: bool = False):
+           arch: Optional[str] = "sm100", autotune: Optional[bool] = True, cudagraph: bool = False,
+           residual: Optional[torch.Tensor] = None):
     """Reduction-width routed projection; signature of the reference's ``gemm_k``
     (``python/gemm_k/jit.py:345-425``).  Returns ``(D[B,T,N], metadata)``; ``D`` is
-    overwritten."""
+    overwritten.
+
+    ``residual`` (extension): a ``[B,T,N]`` tensor added to the projection in fp32 before the
+    single rounding -- the skip connection of the sub-block in the same pass.  Passing ``D``
+    itself gives the accumulate-onto-``D`` behaviour of the reference's CuTe path
+    (``python/gemm_k/jit.py:368``)."""
     assert A.dim() == 3 and B.dim() == 2
     assert Mask.dim() in (2, 3)
     assert estimate_sparsity <= 1
@@ -354,6 +360,13 @@ def gemm_k(A: torch.Tensor, B: torch.Tensor, Mask: torch.Tensor, D: Optional[tor
     lib = N.load()
     m8 = _mask_bytes(Mask.flatten(0, 1))
     metadata: Dict[str, torch.Tensor] = {}
+    R2 = None
+    if residual is not None:
+        if residual.shape[-1] != Nw or residual.numel() != M * Nw or residual.dtype != A.dtype:
+            raise ValueError("residual must have the shape and dtype of the output")
+        R2 = residual.reshape(M, Nw)
+        if R2.stride(-1) != 1 or R2.stride(0) % 8 or R2.data_ptr() % 16:
+            R2 = R2.contiguous()
     with torch.cuda.device(dev):
         use_gemv = _use_gemv_k_dispatch(M, G)
         tensor_core_ok = G % 64 == 0 and Nw % 8 == 0
@@ -361,6 +374,8 @@ def gemm_k(A: torch.Tensor, B: torch.Tensor, Mask: torch.Tensor, D: Optional[tor
             N.check(lib.dpk_gemv_routed(A_f.data_ptr(), A_f.stride(0), Bc.data_ptr(), Bc.stride(0),
                                         m8.data_ptr(), D2.data_ptr(), D2.stride(0), M, Nw, K, NG,
                                         code, 0, 1, _stream()))
+            if R2 is not None:
+                D2.add_(R2)                  # the few-row GEMV path has no fused residual
         else:
             words = (NG + 31) // 32
             row_bits = torch.empty((M, words), dtype=torch.int32, device=dev)
@@ -371,7 +386,8 @@ def gemm_k(A: torch.Tensor, B: torch.Tensor, Mask: torch.Tensor, D: Optional[tor
             ws = torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
             N.check(lib.dpk_gemm_k(A_f.data_ptr(), A_f.stride(0), Bc.data_ptr(), Bc.stride(0),
                                    row_bits.data_ptr(), win_bits.data_ptr(), D2.data_ptr(),
-                                   D2.stride(0), M, Nw, K, NG, code, _ptr(ws), nbytes, _stream()))
+                                   D2.stride(0), M, Nw, K, NG, code, _ptr(R2),
+                                   R2.stride(0) if R2 is not None else 0, _ptr(ws), nbytes, _stream()))
         if not use_gemv:
             smask, sidx, _ = _layout_for(Mask, sorted_mask, sorted_indices, (M, NG))
             metadata = dict(sorted_mask=smask, sorted_indices=sidx)

@@ -190,7 +190,7 @@ def run_gemm(args, which):
         af = a.view(M, I)
         kms, _, _ = time_ms(lambda: N.check(lib.dpk_gemm_k(
             af.data_ptr(), I, wd.data_ptr(), I, rb.data_ptr(), wb.data_ptr(), out.data_ptr(), H,
-            M, H, I, NG, N.BF16, None, 0, st)), args.reps)
+            M, H, I, NG, N.BF16, None, 0, None, 0, st)), args.reps)
     ach = flops / (kms * 1e-3) / 1e12
     return {"kernel": which, "workload": f"M={M} H={H} I={I} NG={NG}x128 top-{keep}",
             "native_call_ms": kms, "ms": ms, "ms_q20": lo, "ms_q80": hi,

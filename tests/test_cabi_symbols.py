@@ -52,10 +52,10 @@ def test_argument_checks_reject_before_any_launch(lib):
     rc = lib.dpk_gemm_mn(p, 128, p, None, 128, p, p, p, 250, 8, 250, 128, 4, N.BF16, 0, None)
     assert rc == N.ERR_INVALID and "divisible" in N.last_error()
     # group width that the tensor-core path does not take
-    rc = lib.dpk_gemm_k(p, 96, p, 96, p, p, p, 64, 8, 64, 96, 2, N.BF16, None, 0, None)
+    rc = lib.dpk_gemm_k(p, 96, p, 96, p, p, p, 64, 8, 64, 96, 2, N.BF16, None, 0, None, 0, None)
     assert rc == N.ERR_INVALID and "multiple of 64" in N.last_error()
     # unknown dtype
-    rc = lib.dpk_gemm_k(p, 128, p, 128, p, p, p, 64, 8, 64, 128, 2, 7, None, 0, None)
+    rc = lib.dpk_gemm_k(p, 128, p, 128, p, p, p, 64, 8, 64, 128, 2, 7, None, 0, None, 0, None)
     assert rc == N.ERR_INVALID
     # head_dim outside {64,128}
     rc = lib.dpk_attn_prefill(p, p, p, p, p, None, p, 1, 16, 16, 4, 2, 96, 2, 0.1, 1, 0, N.BF16, 0, 0, 0, 0, None)

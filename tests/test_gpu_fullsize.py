@@ -153,8 +153,11 @@ def test_config5_layer_full_size(ops):
     conftest.record_strict("config5_attention", O.rel_err(got_a, want_a), f"per-row rms <= {TOL}")
     assert O.rel_err_rows(got_a, want_a) <= TOL
     o, _ = ops.gemm_k(attn.view(1, T, Hq * D), layer.wo, am, **meta)
-    strict("o_projection", o[:, rd], O.gemm_k(f32(attn.view(1, T, Hq * D)[:, rd]), host_w["wo"], amr))
-    x1 = x + o
+    want_o = O.gemm_k(f32(attn.view(1, T, Hq * D)[:, rd]), host_w["wo"], amr)
+    strict("o_projection", o[:, rd], want_o)
+    # the same projection with the skip connection in its epilogue (fp32 sum, one rounding)
+    x1, _ = ops.gemm_k(attn.view(1, T, Hq * D), layer.wo, am, residual=x, **meta)
+    strict("o_projection_plus_residual", x1[:, rd], f32(x[:, rd]) + want_o)
     y = layer.ffn(x1, fm)
     want_y = O.ffn_swiglu(f32(x1[:, rd]), host_w["wg"], host_w["wu"], host_w["wd"], fmr)
     want_y_h = O.ffn_swiglu(f32(x1[:, rd]), host_w["wg"], host_w["wu"], host_w["wd"], fmr,
@@ -166,7 +169,9 @@ def test_config5_layer_full_size(ops):
     conftest.record_strict("config5_ffn", err_y, f"strict <= {TOL} + bf16 rounding floor {floor_y:.3g}; "
                            f"against the oracle with a bf16 intermediate: {O.rel_err(f32(y[:, rd]), want_y_h):.3g}")
     assert err_y <= TOL + floor_y, f"FFN: {err_y:.4g} > {TOL} + {floor_y:.4g}"
-    chained = x1 + y
+    chained = layer.ffn(x1, fm, residual=x1)
+    err_c = O.rel_err(f32(chained[:, rd]), f32(x1[:, rd]) + want_y)
+    assert err_c <= TOL + floor_y, f"FFN + residual: {err_c:.4g}"
     out = layer(x, am, fm)
     assert torch.equal(out, chained), "the layer is not the chain of its operators"
     # the composed layer against the all-fp32 oracle and the measured bf16 hand-off floor

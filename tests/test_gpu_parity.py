@@ -1126,3 +1126,29 @@ def test_prefill_one_and_two_heads_per_cta(ops, B, T, Hq, Hk, D, NG, causal):
     finally:
         _native.check(lib.dpk_set_attn_prefill_heads(0))
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("M,K,N,NG,dtype", [(2500, 512, 512, 4, torch.bfloat16),    # CTA pairs
+                                           (300, 256, 384, 2, torch.float16),      # single CTA
+                                           (64, 2048, 256, 16, torch.bfloat16),    # split group range
+                                           (700, 256, 264, 2, torch.bfloat16)])    # ragged width
+def test_gemm_k_with_residual_in_the_epilogue(ops, M, K, N, NG, dtype):
+    """``D = residual + sum over active groups``: the fp32 sum is rounded once, windows without
+    any active group pass the residual through, and D may be the residual itself."""
+    g = seeded(5)
+    rnd = lambda *s: torch.randn(*s, generator=g).to(dtype).float()
+    a, w, res = rnd(1, M, K), rnd(N, K) / K ** 0.5, rnd(1, M, N)
+    mask = torch.rand(1, M, NG, generator=g) > 0.5
+    mask[0, 128:384] = False                       # whole windows without work
+    want = res + O.gemm_k(a, w, mask)
+    got, _ = ops.gemm_k(dev(a, dtype), dev(w, dtype), dev(mask), residual=dev(res, dtype))
+    assert_rel(got, want)
+    assert torch.equal(got[0, 128:384].float().cpu(), res[0, 128:384])
+    # one rounding of the fp32 sum: never further from it than one unit in the last place of
+    # the output type (adding a rounded projection afterwards can be off by two)
+    ulp = torch.finfo(dtype).eps * want.abs().clamp_min(1e-3)
+    assert bool(((got.float().cpu() - want).abs() <= ulp).all())
+    # in place: D is the residual
+    d = dev(res, dtype).clone()
+    got2, _ = ops.gemm_k(dev(a, dtype), dev(w, dtype), dev(mask), D=d, residual=d)
+    assert got2.data_ptr() == d.data_ptr() and torch.equal(got2, got)
