@@ -621,10 +621,10 @@ def main():
             # NCCL adds bf16 partial sums in bf16 (every rank's partial is rounded, and so is every
             # hop of the reduction), the fused sum adds in fp32 and rounds once: single entries
             # differ by a few bf16 ulps of the largest values (the maximum below), but the RMS of
-            # the difference stays at rounding level.  One misplaced 128-token window out of 16384
-            # tokens would put it near 1e-1, so the RMS bound is the check; the precise check of
-            # the fused output is the "parity" record against the oracle.
-            bound = 5e-3
+            # the difference stays at rounding level (measured 6e-3 at 4 ranks).  One misplaced
+            # 128-token window out of 16384 tokens would put it near 1e-1, so the RMS bound is the
+            # check; the precise check of the fused output is the "parity" record against the oracle.
+            bound = 2e-2
             sum_check = {"fused_vs_nccl_rms_diff_over_rms": rel_rms, "bound": bound,
                          "fused_vs_nccl_max_abs_over_rms": rel_max,
                          "identical_output_on_every_rank": bool(same),
