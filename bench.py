@@ -514,6 +514,9 @@ def main():
     ap.add_argument("--no-configs", action="store_true", help="skip the sub-records of configs 2-4")
     ap.add_argument("--skip-e2e", action="store_true", help="profiler captures only")
     ap.add_argument("--skip-dense", action="store_true", help="profiler captures only")
+    ap.add_argument("--mn-gather", type=int, default=-1, choices=[-1, 0, 1],
+                    help="measurements only: token rows of the output-width GEMM by cp.async (0) or TMA "
+                         "tile::gather4 (1); -1 = the library's default")
     ap.add_argument("--one-block", action="store_true",
                     help="profiler captures only: time a single block of --steps steps")
     args = ap.parse_args()
@@ -541,6 +544,9 @@ def main():
     if world > 1:
         dist.barrier()
     from dpk_b200 import ops, workloads as W
+    if args.mn_gather >= 0:
+        from dpk_b200 import _native
+        _native.check(_native.load().dpk_set_gemm_mn_gather(args.mn_gather))
 
     # ---- sub-records of the other configurations (single GPU), before the long loops of the
     # layer heat the GPU into its power cap: these are sub-millisecond kernels, timed as a burst

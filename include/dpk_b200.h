@@ -174,6 +174,14 @@ int dpk_gemm_mn(const void* A, int64_t lda, const void* W, const void* W2, int64
                 int64_t M, int N, int K, int NG, int dtype, int act, void* stream);
 
 /*
+ * How the CTA-pair form of dpk_gemm_mn brings the gathered token rows into shared memory:
+ * 0 = 16-byte cp.async issued by four warps (reference mechanism:
+ * include/gemm_mn/v1/sm12x.cuh:541-573), 1 = TMA tile::gather4, one warp issuing 32 four-row
+ * copies per 64-wide k-block.  Same results; process-wide, for measurements and tests.
+ */
+int dpk_set_gemm_mn_gather(int mode);
+
+/*
  * Reduction-width routed projection (reference: GEMM_K_V1_Host::run,
  * DynamicPruningKernels/include/gemm_k/v1/sm12x.cuh:738-832; host wrapper
  * python/gemm_k/jit.py:345-425).

@@ -361,6 +361,15 @@ static int pick_bn(int G, int cap)
 
 using namespace dpk;
 
+static int g_mn_gather4 = 0;     // CTA-pair kernel: 0 = token rows by cp.async, 1 = by TMA tile::gather4
+
+extern "C" int dpk_set_gemm_mn_gather(int mode)
+{
+    DPK_REQUIRE(mode == 0 || mode == 1, "mode must be 0 (cp.async row gather) or 1 (TMA tile::gather4)");
+    g_mn_gather4 = mode;
+    return DPK_OK;
+}
+
 extern "C" int dpk_gemm_mn(const void* A, int64_t lda, const void* W, const void* W2, int64_t ldw,
                            const int64_t* sorted_indices, const int32_t* counts, void* D,
                            int64_t ldd, int64_t M, int N, int K, int NG, int dtype, int act,
@@ -419,6 +428,7 @@ extern "C" int dpk_gemm_mn(const void* A, int64_t lda, const void* W, const void
     p.stage_bytes = kAStageBytes * p.halves + umma_n * kBK * 2;
     p.stages = kRingBytes / p.stage_bytes;
     if (p.stages > kMaxStages) p.stages = kMaxStages;
+    p.gather4 = 0;
     p.status = device_status_ptr();
     if (!p.status) return fail(DPK_ERR_CUDA, "no status word on this device");
 
@@ -440,10 +450,15 @@ extern "C" int dpk_gemm_mn(const void* A, int64_t lda, const void* W, const void
             if (rc) return rc;
             MnParams q = p;
             q.halves = 2;
+            // token rows by TMA tile::gather4 (row indices must fit 32 bits, which M does here)
+            CUtensorMap pa;
+            q.gather4 = g_mn_gather4;
+            rc = make_tmap_2d_sw128(&pa, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, kBK, 1);
+            if (rc) return rc;
             const int64_t span_rows = (48ll << 20) / (static_cast<int64_t>(K) * 2);
             int r = static_cast<int>(span_rows / (4 * kBM));
             q.rows_per_block = r < 4 ? 4 : (r > 4096 ? 4096 : r);
-            return gemm_mn_pair_launch(pw, pw2, q, dtype, s);
+            return gemm_mn_pair_launch(pw, pw2, pa, q, dtype, s);
         }
     }
     if (dtype == DPK_BF16) {

@@ -34,6 +34,8 @@ struct MnParams {
                             // fit, so that one weight tile feeds 256 token rows
     int stages;             // ring depth: kRingBytes / stage_bytes, at most kMaxStages
     int stage_bytes;        // kAStageBytes + (UMMA N) * 128
+    int gather4;            // CTA-pair kernel: token rows by TMA tile::gather4 (one warp issues 32
+                            // four-row copies per stage) instead of 16-byte cp.async by four warps
     int* status;
 };
 
@@ -87,7 +89,7 @@ struct TileMap {
 
 // CTA-pair (cta_group::2) variant, dpk_gemm_mn_pair.cu.  Returns DPK_ERR_UNSUPPORTED when the
 // shape is not eligible.
-int gemm_mn_pair_launch(const CUtensorMap& tmW, const CUtensorMap& tmW2, MnParams p, int dtype,
-                        cudaStream_t stream);
+int gemm_mn_pair_launch(const CUtensorMap& tmW, const CUtensorMap& tmW2, const CUtensorMap& tmA,
+                        MnParams p, int dtype, cudaStream_t stream);
 
 }  // namespace dpk

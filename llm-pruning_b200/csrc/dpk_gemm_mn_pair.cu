@@ -32,7 +32,7 @@ constexpr size_t kPairSmemBytes = 1024 + size_t(kRingBytes) + (2 * kMaxStages + 
 template <bool kBf16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMnThreads, 1)
 gemm_mn_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2,
-                    const MnParams p)
+                    const __grid_constant__ CUtensorMap tmA, const MnParams p)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -89,7 +89,9 @@ gemm_mn_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     }
     if (warp == 4 && lane == 0) {
         for (int s = 0; s < kPairStages; ++s) {
-            mbar_init(&full[s], 1 + 256);   // even CTA's expect_tx arrive + 2 x 128 gather threads
+            // even CTA's expect_tx arrive (+ 2 x 128 gather threads when rows come by cp.async;
+            // rows that come by TMA are counted in bytes)
+            mbar_init(&full[s], p.gather4 ? 1 : 1 + 256);
             mbar_init(&empty[s], 1);        // one multicast commit
         }
         for (int b = 0; b < 2; ++b) {
@@ -100,6 +102,7 @@ gemm_mn_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         mbar_init_fence();
         tma_prefetch_desc(&tmW);
         tma_prefetch_desc(&tmW2);
+        if (p.gather4) tma_prefetch_desc(&tmA);
     }
     if (warp == 5) tmem_alloc_pair(tmem_slot, kTmemCols);
     tc_fence_before_sync();
@@ -209,8 +212,10 @@ gemm_mn_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                         break;
                     }
                     uint8_t* sb = smem + size_t(s) * kPairStageBytes + kAStageBytes;
-                    // the even CTA announces the bytes of both halves
-                    if (rank == 0) mbar_arrive_expect_tx(&full[s], 2u * 128 * kBK * 2);
+                    // the even CTA announces the bytes of both halves (and of both CTAs' token
+                    // rows when they come by TMA)
+                    if (rank == 0)
+                        mbar_arrive_expect_tx(&full[s], 2u * 128 * kBK * 2 + (p.gather4 ? 2u * kAStageBytes : 0u));
                     tma_load_2d_pair(sb, map, &full[s], kb * kBK, row0);
                     if (++s == kPairStages) { s = 0; ph ^= 1; }
                 }
@@ -247,6 +252,42 @@ gemm_mn_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                     if (++s == kPairStages) { s = 0; ph ^= 1; }
                 }
                 if (ok) umma_commit_pair(&tfull[ab]);
+            }
+        }
+    } else if (p.gather4) {
+        // ============================ A-row gather by TMA (own 128 rows) =============
+        // one warp: lane l owns rows 4l .. 4l+3 of the tile and issues one four-row copy per
+        // 64-wide k-block; rows past the group's count get an index outside the tensor and
+        // arrive as zeros
+        if (warp == 6) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            const int oob = static_cast<int>(p.M);
+            for (int tile = pair; ok && tile < total_tiles; tile += npairs) {
+                int g, mtile, nchunk;
+                tmap.decode(tile, g, mtile, nchunk);
+                const int cnt = p.counts[g];
+                int r[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int slot = mtile * RT + rank * kBM + 4 * lane + i;
+                    r[i] = oob;
+                    if (slot < cnt) {
+                        const int64_t tok = p.sidx[static_cast<int64_t>(slot) * p.NG + g];
+                        if (tok >= 0 && tok < p.M) r[i] = static_cast<int>(tok);
+                    }
+                }
+                for (int kb = 0; kb < KB; ++kb) {
+                    const bool got = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, DPK_DEV_TIMEOUT_EMPTY);
+                    if (!__all_sync(0xffffffffu, got)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* dst = smem + size_t(s) * kPairStageBytes + lane * (4 * 128);
+                    tma_gather4_pair(dst, &tmA, &full[s], kb * kBK, r[0], r[1], r[2], r[3]);
+                    if (++s == kPairStages) { s = 0; ph ^= 1; }
+                }
             }
         }
     } else {
@@ -319,19 +360,19 @@ gemm_mn_pair_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     }
 }
 
-int gemm_mn_pair_launch(const CUtensorMap& tmW, const CUtensorMap& tmW2, MnParams p, int dtype,
-                        cudaStream_t s)
+int gemm_mn_pair_launch(const CUtensorMap& tmW, const CUtensorMap& tmW2, const CUtensorMap& tmA,
+                        MnParams p, int dtype, cudaStream_t s)
 {
     int grid = sm_count() & ~1;
     if (grid < 2) return fail(DPK_ERR_UNSUPPORTED, "no CTA pair available");
     if (dtype == DPK_BF16) {
         DPK_CUDA(cudaFuncSetAttribute(gemm_mn_pair_kernel<true>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairSmemBytes));
-        gemm_mn_pair_kernel<true><<<grid, kMnThreads, kPairSmemBytes, s>>>(tmW, tmW2, p);
+        gemm_mn_pair_kernel<true><<<grid, kMnThreads, kPairSmemBytes, s>>>(tmW, tmW2, tmA, p);
     } else {
         DPK_CUDA(cudaFuncSetAttribute(gemm_mn_pair_kernel<false>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairSmemBytes));
-        gemm_mn_pair_kernel<false><<<grid, kMnThreads, kPairSmemBytes, s>>>(tmW, tmW2, p);
+        gemm_mn_pair_kernel<false><<<grid, kMnThreads, kPairSmemBytes, s>>>(tmW, tmW2, tmA, p);
     }
     DPK_CUDA(cudaGetLastError());
     return DPK_OK;

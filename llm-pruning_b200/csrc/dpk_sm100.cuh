@@ -339,6 +339,21 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
         "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar) & kPeerMask), "r"(c0), "r"(c1)
         : "memory");
 }
+// Four rows of a 2-D tensor (box of the map: 64 columns x 1 row), given by their row indices,
+// into four consecutive 128-byte rows of this CTA's shared memory; bytes are counted on the
+// even CTA's barrier.  A row index outside the tensor is filled with zeros.  c0 is the
+// (16-byte aligned) column coordinate.
+__device__ __forceinline__ void tma_gather4_pair(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                                 int32_t c0, int32_t r0, int32_t r1, int32_t r2,
+                                                 int32_t r3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile::gather4"
+        ".mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar) & kPeerMask), "r"(c0), "r"(r0), "r"(r1),
+        "r"(r2), "r"(r3)
+        : "memory");
+}
 __device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                                  uint32_t idesc, uint32_t accumulate)
 {

@@ -370,6 +370,18 @@ def gemm_k(A: torch.Tensor, B: torch.Tensor, Mask: torch.Tensor, D: Optional[tor
     with torch.cuda.device(dev):
         use_gemv = _use_gemv_k_dispatch(M, G)
         tensor_core_ok = G % 64 == 0 and Nw % 8 == 0
+        if (NG == 1 and R2 is None and not use_gemv and M >= 256 and Nw % 16 == 0 and K % 8 == 0
+                and D2.is_contiguous()):
+            # A whole-token mask (one group spanning all of K; LFF's token gate) is the same
+            # product as an output-width routed projection with one group spanning all of N: the
+            # active rows are compacted, so no MMA row is spent on a skipped token (the masked
+            # kernel below only skips whole 128-token windows).  Skipped rows are zero.
+            smask, sidx, counts = _layout_for(Mask, sorted_mask, sorted_indices, (M, NG))
+            D2.zero_()
+            N.check(lib.dpk_gemm_mn(A_f.data_ptr(), A_f.stride(0), Bc.data_ptr(), None, Bc.stride(0),
+                                    sidx.data_ptr(), counts.data_ptr(), D2.data_ptr(), D2.stride(0),
+                                    M, Nw, K, 1, code, N.ACT["identity"], _stream()))
+            return D2.reshape(Bsz, T, Nw), dict(sorted_mask=smask, sorted_indices=sidx)
         if use_gemv or not tensor_core_ok:
             N.check(lib.dpk_gemv_routed(A_f.data_ptr(), A_f.stride(0), Bc.data_ptr(), Bc.stride(0),
                                         m8.data_ptr(), D2.data_ptr(), D2.stride(0), M, Nw, K, NG,

@@ -283,11 +283,15 @@ def main(argv=None):
     ap.add_argument("--tokens", type=int, default=0, help="override the token / KV length")
     ap.add_argument("--batch", type=int, default=0, help="override the decode batch")
     ap.add_argument("--fp16", action="store_true", help="attention_prefill: fp16 tensors instead of bf16")
+    ap.add_argument("--gather4", type=int, default=-1, choices=[-1, 0, 1],
+                    help="gemm_mn / ffn: token rows by cp.async (0) or TMA tile::gather4 (1); -1 = the default")
     ap.add_argument("--heads-per-cta", type=int, default=0, choices=[0, 1, 2],
                     help="attention_prefill: 2 = the two-heads-per-CTA kernel, 0/1 = one head per CTA")
     args = ap.parse_args(argv)
     assert torch.cuda.is_available(), "dpk_b200.perf needs a CUDA device"
     _native.check(_native.load().dpk_set_attn_prefill_heads(args.heads_per_cta))
+    if args.gather4 >= 0:
+        _native.check(_native.load().dpk_set_gemm_mn_gather(args.gather4))
     if args.kernel == "attention_prefill":
         res = run_prefill(args)
     elif args.kernel == "attention_decode":

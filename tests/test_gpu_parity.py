@@ -1153,3 +1153,48 @@ def test_gemm_k_with_residual_in_the_epilogue(ops, M, K, N, NG, dtype):
     d = dev(res, dtype).clone()
     got2, _ = ops.gemm_k(dev(a, dtype), dev(w, dtype), dev(mask), D=d, residual=d)
     assert got2.data_ptr() == d.data_ptr() and torch.equal(got2, got)
+
+
+@pytest.mark.parametrize("M,K,N,keep", [(3000, 1024, 512, 0.3), (2048, 512, 384, 0.9)])
+def test_gemm_k_whole_token_mask_takes_compacted_rows(ops, M, K, N, keep):
+    """One group spanning all of K (LFF's token gate): the projection runs over the compacted
+    active rows; skipped tokens come out exactly zero, with and without a caller's D."""
+    bf = torch.bfloat16
+    g = seeded(13)
+    a, w = bf16r(torch.randn(1, M, K, generator=g)), bf16r(torch.randn(N, K, generator=g) / K ** 0.5)
+    mask = torch.rand(1, M, generator=g) < keep
+    want = O.gemm_k(a, w, mask)
+    got, meta = ops.gemm_k(dev(a, bf), dev(w, bf), dev(mask))
+    assert_rel_active(got, want)
+    assert float(got[0][~dev(mask)[0]].abs().max()) == 0.0
+    assert set(meta) == {"sorted_mask", "sorted_indices"}
+    d = torch.full((1, M, N), 7.0, dtype=bf, device="cuda")
+    got2, _ = ops.gemm_k(dev(a, bf), dev(w, bf), dev(mask), D=d, **meta)
+    assert got2.data_ptr() == d.data_ptr() and torch.equal(got2, got)
+
+
+@pytest.mark.parametrize("M,K,N,NG,fused", [(4100, 512, 1024, 4, False), (2100, 200, 512, 2, False),
+                                           (8192, 1024, 2048, 16, True)])
+def test_gemm_mn_rows_by_tma_gather4(ops, M, K, N, NG, fused):
+    """The CTA-pair kernel with its token rows brought in by TMA tile::gather4 instead of
+    cp.async: same bits, ragged K (200 is not a multiple of 64) and ragged last tiles included."""
+    from dpk_b200 import _native
+
+    bf = torch.bfloat16
+    g = seeded(17)
+    a = bf16r(torch.randn(1, M, K, generator=g))
+    w = bf16r(torch.randn(N, K, generator=g) / K ** 0.5)
+    w2 = bf16r(torch.randn(N, K, generator=g) / K ** 0.5) if fused else None
+    mask = torch.rand(1, M, NG, generator=g) > 0.5
+    lib = _native.load()
+    outs = []
+    try:
+        for mode in (0, 1):
+            _native.check(lib.dpk_set_gemm_mn_gather(mode))
+            out, _ = ops.gemm_mn(dev(a, bf), dev(w, bf), dev(mask), up_weight=dev(w2, bf) if fused else None)
+            outs.append(out)
+    finally:
+        _native.check(lib.dpk_set_gemm_mn_gather(0))
+    assert torch.equal(outs[0], outs[1])
+    want = O.gemm_mn(a, w, mask, "silu") * O.gemm_mn(a, w2, mask) if fused else O.gemm_mn(a, w, mask)
+    assert_rel_active(outs[1], want, tol=4e-2 if fused else TOL)
