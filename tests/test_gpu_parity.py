@@ -1197,4 +1197,6 @@ def test_gemm_mn_rows_by_tma_gather4(ops, M, K, N, NG, fused):
         _native.check(lib.dpk_set_gemm_mn_gather(0))
     assert torch.equal(outs[0], outs[1])
     want = O.gemm_mn(a, w, mask, "silu") * O.gemm_mn(a, w2, mask) if fused else O.gemm_mn(a, w, mask)
-    assert_rel_active(outs[1], want, tol=4e-2 if fused else TOL)
+    # the silu(gate)*up product is heavy-tailed: half a bf16 ulp of its largest entries is what
+    # this bound has to leave room for (as in test_gemm_mn_cta_pairs)
+    assert_rel_active(outs[1], want, tol=8e-2 if fused else TOL)
