@@ -58,6 +58,7 @@ class RoutedDecoderLayer:
         self.qkv_group = math.gcd(math.gcd(qd // attn_groups, 2 * kd), 256)
         self.fold_qkv = self.qkv_group >= 64
         self._qkv_out = None
+        self._attn_out = None
         self.ffn = RoutedFFN(wg, wu, wd, ffn_groups, max_tokens)
         self.pg = process_group
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
@@ -109,7 +110,7 @@ class RoutedDecoderLayer:
         q, k, v = self.project_qkv(h, am)
         ops.rope_append(q, k, None, cos, sin)
         self._mark("qkv")
-        attn, meta = ops.attention_prefill(q, k, v, am)
+        attn, meta = ops.attention_prefill(q, k, v, am, O=self._attention_out(B, T, q))
         if B != 1:
             meta = {}        # per-batch layout (attention) vs flattened layout (GEMMs)
         self._mark("attn")
@@ -168,6 +169,16 @@ class RoutedDecoderLayer:
                 out[..., qd:qd + kd].view(B, T, self.Hk, self.D),
                 out[..., qd + kd:].view(B, T, self.Hk, self.D))
 
+    def _attention_out(self, B: int, T: int, like: torch.Tensor) -> torch.Tensor:
+        """Output buffer of the attention call, allocated once and NOT zero-filled: the rows of
+        routed-out (token, head group) pairs stay unwritten, and the output projection that
+        reads this buffer never uses them (it clears the rows of inactive groups in shared
+        memory instead of multiplying what it loaded)."""
+        n = B * T * self.Hq * self.D
+        if self._attn_out is None or self._attn_out.numel() < n or self._attn_out.dtype != like.dtype:
+            self._attn_out = torch.empty(n, dtype=like.dtype, device=like.device)
+        return self._attn_out[:n].view(B, T, self.Hq, self.D)
+
     def _mark(self, name):
         if self.timers is not None:
             ev = torch.cuda.Event(enable_timing=True)
@@ -186,7 +197,7 @@ class RoutedDecoderLayer:
         self._mark("start")
         q, k, v = self.project_qkv(x, attn_mask)
         self._mark("qkv")
-        attn, meta = ops.attention_prefill(q, k, v, attn_mask)
+        attn, meta = ops.attention_prefill(q, k, v, attn_mask, O=self._attention_out(B, T, q))
         if B != 1:
             meta = {}        # per-batch layout (attention) vs flattened layout (GEMMs)
         self._mark("attn")

@@ -349,7 +349,9 @@ def gemm_k(A: torch.Tensor, B: torch.Tensor, Mask: torch.Tensor, D: Optional[tor
         raise ValueError("A and B disagree on K")
     Bc = B if B.stride(-1) == 1 and B.stride(0) % 8 == 0 else B.contiguous()
     if D is None:
-        D = torch.zeros((M, Nw), dtype=A.dtype, device=dev)
+        # every path below writes every element of D (rows without an active group come out
+        # as zeros, or as the residual), so a fresh output needs no zero-fill
+        D = torch.empty((M, Nw), dtype=A.dtype, device=dev)
     D2 = D.view(M, Nw)
     if Mask.dim() == 2:
         Mask = Mask.unsqueeze(-1)

@@ -29,8 +29,8 @@ def pytest_collection_modifyitems(config, items):
 # The tolerance is stated as max|err| <= 2e-2 * rms(whole expected output).  Where a test
 # asserts a refined form instead (RMS over the non-zero entries, per-row RMS, a wider bound on
 # an intermediate), it also records the strict-form number here; the numbers are printed in
-# the terminal summary and written to a JSON file so that the distance from the stated bound
-# is on record.
+# the terminal summary and written to a JSON file (the path in DPK_PARITY_REPORT, else pytest's
+# cache directory) so that the distance from the stated bound is on record.
 
 STRICT = {}
 
@@ -56,9 +56,9 @@ def pytest_terminal_summary(terminalreporter, exitstatus, config):
         tr.write_line(f"{rec['max_abs_over_global_rms']:9.4g}  {key}  [{rec['asserted']}]")
     path = os.environ.get("DPK_PARITY_REPORT")
     if not path:
-        out_dir = os.path.join(ROOT, "gpurun_out")
-        if os.path.isdir(out_dir):
-            path = os.path.join(out_dir, "parity_strict_metrics.json")
+        cache = os.path.join(ROOT, ".pytest_cache")
+        if os.path.isdir(cache):
+            path = os.path.join(cache, "parity_strict_metrics.json")
     if path:
         try:
             with open(path, "w") as f:

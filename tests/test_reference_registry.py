@@ -14,7 +14,9 @@ import tempfile
 
 import pytest
 
-REF_ROOT = os.environ.get("DPK_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: named by DPK_REFERENCE_ROOT, else a directory "reference" beside this repository
+REF_ROOT = os.environ.get("DPK_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 REF_PKG = os.path.join(REF_ROOT, "DynamicPruningKernels", "python")
 FAMILIES = ("gemm_mn", "gemm_k", "attention_prefill", "attention_decode")
 
