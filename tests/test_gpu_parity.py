@@ -1152,7 +1152,14 @@ def test_gemm_k_with_residual_in_the_epilogue(ops, M, K, N, NG, dtype):
     # in place: D is the residual
     d = dev(res, dtype).clone()
     got2, _ = ops.gemm_k(dev(a, dtype), dev(w, dtype), dev(mask), D=d, residual=d)
-    assert got2.data_ptr() == d.data_ptr() and torch.equal(got2, got)
+    assert got2.data_ptr() == d.data_ptr()
+    if M > 512:
+        assert torch.equal(got2, got)
+    else:
+        # few windows: the group range is split over CTAs that add fp32 partial sums with red.add,
+        # in an order that varies from launch to launch; an entry on a rounding boundary may then
+        # land on either side of it
+        torch.testing.assert_close(got2.float(), got.float(), rtol=2 * torch.finfo(dtype).eps, atol=1e-6)
 
 
 @pytest.mark.parametrize("M,K,N,keep", [(3000, 1024, 512, 0.3), (2048, 512, 384, 0.9)])
