@@ -456,6 +456,18 @@ def sub_decode(dev, steps, peaks):
     f_blocks = timed_blocks(lambda: ffn(x, fmask, out=y), steps, 5, 1, dev, seconds=0.2, min_blocks=5,
                             max_blocks=20)
     a_ms, f_ms = statistics.median(a_blocks), statistics.median(f_blocks)
+    # the same two calls as ONE CUDA graph, replayed: how the reference times its kernels
+    # (gemm_mn/jit.py:619-631), and what a decode loop would launch per layer
+    graph_ms = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            ops.attention_decode(q, k, v, amask, O=o)
+            ffn(x, fmask, out=y)
+        graph_ms = statistics.median(timed_blocks(graph.replay, steps, 5, 1, dev, seconds=0.4, min_blocks=5,
+                                                  max_blocks=20))
+    except Exception as exc:       # capture is an extra, not the measurement
+        print(f"bench: CUDA graph capture of the decode step failed: {exc}", file=sys.stderr)
     sdpa = torch.nn.functional.scaled_dot_product_attention
     qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
     d_ms = statistics.median(timed_blocks(lambda: sdpa(qt, kt, vt, enable_gqa=True), steps, 3, 1, dev,
@@ -478,6 +490,7 @@ def sub_decode(dev, steps, peaks):
     wantf = O.ffn_swiglu(x.float().cpu(), wg.float().cpu(), wu.float().cpu(), wd.float().cpu(), fmask.cpu())
     errf = strict_err(y.view(f.tokens, 1, f.hidden), wantf)
     return {"workload": sh.name, "tpot_us": (a_ms + f_ms) * 1e3, "attention_us": a_ms * 1e3, "ffn_us": f_ms * 1e3,
+            "tpot_cuda_graph_us": graph_ms * 1e3 if graph_ms else None,
             "dense_sdpa_us": d_ms * 1e3, "attention_speedup_vs_dense": d_ms / a_ms,
             "floor_us": (a_bytes + f_bytes) / (hbm * 1e9) * 1e6,
             "roofline": {"kernel": "attn_decode_kernel", "bound": "hbm", "achieved": a_gbs, "peak": hbm,

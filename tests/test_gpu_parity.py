@@ -1207,3 +1207,54 @@ def test_gemm_mn_rows_by_tma_gather4(ops, M, K, N, NG, fused):
     # the silu(gate)*up product is heavy-tailed: half a bf16 ulp of its largest entries is what
     # this bound has to leave room for (as in test_gemm_mn_cta_pairs)
     assert_rel_active(outs[1], want, tol=8e-2 if fused else TOL)
+
+
+def test_calls_are_cuda_graph_capturable(ops):
+    """The reference runs its kernels under CUDA graphs (``cudagraph=True`` in every benchmark,
+    ``python/gemm_mn/jit.py:223, 629``), so every call has to be stream-ordered and free of
+    synchronisation: capture a prefill FFN, a decode-sized FFN and a decode attention call once
+    (after a warm-up call, which resolves per-device state), replay them on new inputs written
+    into the same buffers, and compare with eager calls."""
+    from dpk_b200.ffn import RoutedFFN
+
+    bf = torch.bfloat16
+    g = seeded(3)
+    H, I, NG = 512, 2048, 16
+    wg, wu, wd = (dev(bf16r(torch.randn(*s, generator=g) * 0.05), bf) for s in ((I, H), (I, H), (H, I)))
+    cases = []
+    for M in (700, 48):                                    # prefill kernels / the two-launch decode path
+        ffn = RoutedFFN(wg, wu, wd, NG, M)
+        x = dev(bf16r(torch.randn(M, H, generator=g)), bf)
+        mask = dev(torch.rand(M, NG, generator=g) > 0.5)
+        y = torch.empty(M, H, dtype=bf, device="cuda")
+        # the decode-sized path adds fp32 partial sums with red.add: the last bit depends on the order
+        cases.append((lambda ffn=ffn, x=x, mask=mask, y=y: ffn(x, mask, out=y), (x, mask), y, M > 128))
+    B, Tk, Hq, Hk, D = 3, 700, 8, 2, 128
+    q = dev(bf16r(torch.randn(B, 1, Hq, D, generator=g)), bf)
+    k = dev(bf16r(torch.randn(B, Tk, Hk, D, generator=g)), bf)
+    v = dev(bf16r(torch.randn(B, Tk, Hk, D, generator=g)), bf)
+    dm = dev(torch.rand(B, 1, 2, generator=g) > 0.3)
+    o = torch.empty_like(q)
+    cases.append((lambda: ops.attention_decode(q, k, v, dm, O=o), (q, k), o, True))
+
+    side = torch.cuda.Stream()
+    for call, inputs, out, exact in cases:
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            call()                                          # warm-up outside the capture
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            call()
+        for t in inputs:                                    # new inputs, same buffers
+            if t.dtype == torch.bool:
+                t.copy_(torch.rand(t.shape, device="cuda") > 0.5)
+            else:
+                t.copy_(torch.randn(t.shape, device="cuda").to(t.dtype))
+        graph.replay()
+        replayed = out.clone()
+        call()
+        if exact:
+            assert torch.equal(replayed, out)
+        else:
+            torch.testing.assert_close(replayed.float(), out.float(), rtol=2 ** -6, atol=1e-3)
