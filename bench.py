@@ -522,6 +522,9 @@ def main():
     ap.add_argument("--halves", type=int, default=2, choices=[1, 2],
                     help="--sum fused: 2 = project the tokens in two halves and gather the first half "
                          "under the second half's projection")
+    ap.add_argument("--barrier", choices=["nccl", "flags"], default="nccl",
+                    help="--sum fused: what separates the two kernels of a sum on the stream: a "
+                         "one-element NCCL all-reduce, or dpk_peer_barrier (flags in peer memory)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the sub-records of configs 2-4")
@@ -622,6 +625,7 @@ def main():
             try:
                 layer.fuse_sums(T)
                 layer.sum_o.halves = layer.ffn.row_parallel.halves = args.halves
+                layer.sum_o.barrier_mode = layer.ffn.row_parallel.barrier_mode = args.barrier
                 fused = True
             except RuntimeError as exc:       # the same exception on every rank (see connect)
                 if rank == 0:
@@ -860,7 +864,7 @@ def main():
         "config": make_config(shape, world, args),
         "timing": {"blocks": len(blocks), "steps_per_block": args.steps, "ms_per_step_p20_p80": [ms_lo, ms_hi],
                    "how": "median over blocks of (max over ranks of a block's device time) / steps"},
-        "sums": ("fused row-parallel sums, tokens in %d part(s)" % args.halves) if fused else
+        "sums": ("fused row-parallel sums, tokens in %d part(s), %s barriers" % (args.halves, args.barrier)) if fused else
                 ("NCCL all-reduce" if world > 1 else None),
         "algorithmic_tflop_per_step": flops / 1e12,
         "layer_roofline": {"achieved": flops / (ms_step * 1e-3) / 1e12, "peak": sus * world, "unit": "TFLOP/s",

@@ -353,7 +353,8 @@ int dpk_rope_append(void* q, void* k, const void* v, const void* cos, const void
  *      `rank` of the owner's staging buffer stage[o], laid out [world, R, ldd] -- stores
  *      into peer memory, overlapped with the tiles still being computed.
  *   2. the caller makes sure every rank has finished step 1 (any barrier between ranks
- *      that is ordered after the kernel on `stream`, e.g. a one-element all-reduce);
+ *      that is ordered after the kernel on `stream`: dpk_peer_barrier, or a one-element
+ *      all-reduce);
  *   3. dpk_reduce_gather on every rank: adds the `world` slabs of the rows it owns in
  *      fp32 (+ an optional residual [M,ld]), rounds once and stores the rows into every
  *      rank's out[j] ([M,ld]);
@@ -368,6 +369,20 @@ int dpk_peer_alloc(size_t bytes, void** ptr, void* handle);
 int dpk_peer_open(const void* handle, void** ptr);
 int dpk_peer_close(void* ptr);
 int dpk_peer_free(void* ptr);
+
+/*
+ * Barrier between the ranks through flags in peer-mapped memory, as one small kernel on
+ * `stream` (no counterpart in the reference).  Each rank owns `world` 32-bit slots, zero before
+ * the first use; peer_flags: host array of `world` device pointers to every rank's slot array
+ * (peer_flags[rank] == my_flags).  The kernel publishes this rank's arrival (epoch) to every
+ * rank, ordered after everything earlier work of the stream wrote to peer memory, and waits
+ * until every rank's arrival for the same epoch is visible here.  epoch has to grow by one per
+ * barrier, identically on all ranks.  The wait gives up after timeout_ms: the status word is
+ * set (code 107, kernel 8), the kernel returns, the context stays usable and the data of that
+ * step must be discarded.  Every rank has to run on a GPU of its own.
+ */
+int dpk_peer_barrier(void* const* peer_flags, void* my_flags, int world, int rank, uint32_t epoch,
+                     int timeout_ms, void* stream);
 
 size_t dpk_gemm_k_scatter_workspace_bytes(int64_t M, int N, int64_t ldd);
 

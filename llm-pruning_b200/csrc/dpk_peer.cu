@@ -79,9 +79,75 @@ __global__ void __launch_bounds__(256) reduce_gather_kernel(const ReduceGatherPa
     }
 }
 
+// Barrier between the ranks of one node through flags in peer-mapped memory.  Every rank owns
+// an array of `world` 32-bit slots; slot s of rank o's array is written only by rank s.  Thread j
+// of the single block publishes this rank's arrival to rank j (a system-scope release store of
+// the epoch number into slot `rank` of j's array: everything this rank wrote to peer memory
+// before the kernel -- earlier kernels of the same stream included -- is visible to whoever
+// observes the store) and then waits until slot j of its OWN array has reached the epoch.  The
+// wait is bounded: after `limit_cycles` it records a status code and the kernel returns, so the
+// context stays usable; the caller must treat the step's result as invalid then.  Epochs only
+// grow, so a rank that is one barrier ahead cannot be mistaken for one that has arrived at this
+// one, and no slot is ever reset.  Every rank runs this kernel on its own GPU.
+struct PeerFlagTable {
+    uint32_t* p[kMaxPeersRG];
+};
+
+__global__ void __launch_bounds__(32) peer_barrier_table_kernel(const PeerFlagTable peer_flags,
+                                                                uint32_t* my_flags, int world, int rank,
+                                                                uint32_t epoch, long long limit_cycles,
+                                                                int* status)
+{
+    const int j = threadIdx.x;
+    if (j >= world) return;
+    __threadfence_system();
+    uint32_t* remote = peer_flags.p[j] + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+    const uint32_t* mine = my_flags + j;
+    const long long t0 = clock64();
+    uint32_t seen;
+    while (true) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        if (static_cast<int32_t>(seen - epoch) >= 0) break;
+        if (clock64() - t0 > limit_cycles) {
+            atomicCAS(status, 0, 1000 * DPK_KERNEL_ID + DPK_DEV_TIMEOUT_PEER);
+            break;
+        }
+        __nanosleep(200);
+    }
+    __threadfence_system();
+}
+
 }  // namespace dpk
 
 using namespace dpk;
+
+extern "C" int dpk_peer_barrier(void* const* peer_flags, void* my_flags, int world, int rank,
+                                uint32_t epoch, int timeout_ms, void* stream)
+{
+    DPK_REQUIRE(peer_flags && my_flags, "NULL flags");
+    DPK_REQUIRE(world >= 1 && world <= kMaxPeersRG && rank >= 0 && rank < world, "bad world / rank");
+    DPK_REQUIRE(timeout_ms > 0 && timeout_ms <= 10000, "timeout_ms must be 1..10000");
+    DPK_REQUIRE((reinterpret_cast<uintptr_t>(my_flags) & 3u) == 0, "flags must be 4-byte aligned");
+    int* status = device_status_ptr();
+    if (!status) return fail(DPK_ERR_CUDA, "no status word on this device");
+    // the table of peer pointers travels as a kernel argument: no device allocation
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    PeerFlagTable t;
+    for (int i = 0; i < kMaxPeersRG; ++i) t.p[i] = nullptr;
+    for (int i = 0; i < world; ++i) {
+        DPK_REQUIRE(peer_flags[i] && (reinterpret_cast<uintptr_t>(peer_flags[i]) & 3u) == 0, "flag array %d", i);
+        t.p[i] = static_cast<uint32_t*>(peer_flags[i]);
+    }
+    int dev = 0, khz = 0;
+    DPK_CUDA(cudaGetDevice(&dev));
+    DPK_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));
+    const long long limit = static_cast<long long>(khz > 0 ? khz : 2000000) * timeout_ms;
+    peer_barrier_table_kernel<<<1, 32, 0, s>>>(t, static_cast<uint32_t*>(my_flags), world, rank, epoch,
+                                              limit, status);
+    DPK_CUDA(cudaGetLastError());
+    return DPK_OK;
+}
 
 extern "C" int dpk_peer_alloc(size_t bytes, void** ptr, void* handle)
 {

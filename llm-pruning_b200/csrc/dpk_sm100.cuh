@@ -23,6 +23,7 @@ enum : int {
     DPK_DEV_TIMEOUT_TMEM_EMPTY = 104,
     DPK_DEV_BAD_INDEX = 105,        // a routing index pointed outside the token range
     DPK_DEV_BAD_SMEM_BASE = 106,    // dynamic shared memory was not 1024-byte aligned
+    DPK_DEV_TIMEOUT_PEER = 107,     // a peer rank's arrival flag did not show up within the limit
 };
 
 // about one second at 2 GHz

@@ -56,6 +56,7 @@ SIGNATURES = {
                                _i32, _i32, _i32, _i32, _i32, _vp]),
     "dpk_rope_append": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i32, _i32, _i32, _i32, _i32,
                                _i64, _i64, _i32, _i64, _i64, _vp]),
+    "dpk_peer_barrier": (_i32, [C.POINTER(_vp), _vp, _i32, _i32, C.c_uint32, _i32, _vp]),
     "dpk_peer_alloc": (_i32, [_sz, C.POINTER(_vp), _vp]),
     "dpk_peer_open": (_i32, [_vp, C.POINTER(_vp)]),
     "dpk_peer_close": (_i32, [_vp]),

@@ -7,8 +7,10 @@ sums to local memory and handing them to an all-reduce, the projection kernel st
 128-token window straight into the memory of the rank that owns those rows while the other
 tiles are still being computed; each owner then adds the slabs it received (fp32, optional
 residual) and stores the finished rows into every rank's output.  Between the two kernels,
-and after the second, the ranks meet at a barrier (a one-element all-reduce, ordered on
-the stream) -- no kernel waits on another GPU.
+and after the second, the ranks meet at a barrier ordered on the stream: a one-element NCCL
+all-reduce (``barrier_mode = "nccl"``, the default) or ``dpk_peer_barrier``, one small kernel
+per rank that publishes an arrival flag in every peer's memory and waits, with a time limit,
+for the peers' flags (``barrier_mode = "flags"``).
 
 Buffers come from the C library (``dpk_peer_alloc``) and are mapped into the peers with
 CUDA IPC; the 64-byte handles travel through ``torch.distributed``.
@@ -32,6 +34,7 @@ from .ops import _mask_bytes, _stream
 
 MAX_WORLD = 8
 WINDOW = 128
+FLAG_BYTES = 256            # arrival slots of the flag barrier, at the end of the peer buffer
 
 
 def rows_per_owner(M: int, world: int) -> int:
@@ -90,15 +93,20 @@ class RowParallelSum:
     (a view into the peer-visible buffer, valid until the next call).
     """
 
+    barrier_mode = "nccl"        # or "flags": see the module docstring
+    barrier_timeout_ms = 2000    # flag barrier: how long a rank waits for its peers
+
     def __init__(self, world: int, rank: int, max_rows: int, width: int, dtype: torch.dtype,
                  device: torch.device, stage: torch.Tensor, out: torch.Tensor,
                  stage_ptrs: Sequence[int], out_ptrs: Sequence[int],
-                 barrier: Callable[[], None], keep=()):
+                 barrier: Callable[[], None], keep=(), flag_ptrs: Sequence[int] = ()):
         self.world, self.rank, self.max_rows, self.width = world, rank, max_rows, width
         self.dtype, self.device = dtype, device
         self.stage, self.out = stage, out
         self._stage_ptrs, self._out_ptrs = list(stage_ptrs), list(out_ptrs)
-        self._barrier = barrier
+        self._nccl_barrier = barrier
+        self._flag_ptrs = list(flag_ptrs)       # every rank's arrival slots (peer-mapped), or empty
+        self._epoch = 0
         self.halves = 1          # 2: split the tokens; the second half's projection hides the first half's gather
         self._side = None
         self._keep = keep
@@ -106,6 +114,16 @@ class RowParallelSum:
         self.code = 1 if dtype == torch.bfloat16 else 0
         self._ws = None
         self.timers = None      # dict -> lists of CUDA events at the five points of a fused sum
+
+    def _barrier(self) -> None:
+        """All ranks have finished what they enqueued before this point (stream-ordered)."""
+        if self.barrier_mode == "flags" and self._flag_ptrs:
+            self._epoch += 1
+            N.check(self.lib.dpk_peer_barrier(_ptr_table(self._flag_ptrs), self._flag_ptrs[self.rank],
+                                              self.world, self.rank, self._epoch,
+                                              int(self.barrier_timeout_ms), _stream()))
+        else:
+            self._nccl_barrier()
 
     # ---- construction -----------------------------------------------------------------
     @staticmethod
@@ -129,7 +147,7 @@ class RowParallelSum:
             base = C.c_void_p()
             handle = C.create_string_buffer(64)
             try:
-                N.check(lib.dpk_peer_alloc(2 * nbytes, C.byref(base), handle))
+                N.check(lib.dpk_peer_alloc(2 * nbytes + FLAG_BYTES, C.byref(base), handle))
             except Exception as exc:          # noqa: BLE001 - reported to all ranks below
                 problem = f"rank {rank}: {exc}"
             handles: List[Optional[bytes]] = [None] * world
@@ -158,16 +176,20 @@ class RowParallelSum:
                 if base.value:
                     lib.dpk_peer_free(base)
                 raise RuntimeError("peer buffers unavailable: " + "; ".join(x for x in problems if x))
-            raw = torch.as_tensor(_DeviceBytes(base.value, 2 * nbytes), device=device)
+            raw = torch.as_tensor(_DeviceBytes(base.value, 2 * nbytes + FLAG_BYTES), device=device)
         stage = raw[:nbytes].view(dtype)
-        out = raw[nbytes:].view(dtype)
+        out = raw[nbytes:2 * nbytes].view(dtype)
+        raw[2 * nbytes:].zero_()                 # arrival slots start at zero on every rank ...
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)                # ... before any rank can publish into them
         token = torch.zeros(1, device=device)
 
         def barrier():
             dist.all_reduce(token, group=group)
 
         self = cls(world, rank, max_rows, width, dtype, device, stage, out, bases,
-                   [b + nbytes for b in bases], barrier, keep=(raw, token))
+                   [b + nbytes for b in bases], barrier, keep=(raw, token),
+                   flag_ptrs=[b + 2 * nbytes for b in bases])
         self._mapped = [b for r, b in enumerate(bases) if r != rank]
         self._owned = base.value
         return self

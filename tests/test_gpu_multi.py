@@ -60,9 +60,19 @@ def _worker(rank, world, port, ret):
         for _ in range(3):
             y = ffn(xd, lmask, residual=xd)
         torch.cuda.synchronize()
+        # the same schedule with the barriers as flags in peer memory instead of NCCL all-reduces
+        ffn.row_parallel.barrier_mode = "flags"
+        for _ in range(4):
+            y_flags = ffn(xd, lmask, residual=xd)
+        torch.cuda.synchronize()
+        flags_equal = bool(torch.equal(y_flags, y_one))
+        ffn.row_parallel.barrier_mode = "nccl"
+        y = ffn(xd, lmask, residual=xd)
+        torch.cuda.synchronize()
         want = x.float() + O.ffn_swiglu(x.float(), wg.float(), wu.float(), wd.float(), mask,
                                         round_intermediate=bf)
         ret[rank] = dict(
+            flags_equal=flags_equal,
             vs_nccl=O.rel_err(y.float().cpu(), y_nccl.float().cpu()),
             vs_oracle=O.rel_err(y.float().cpu(), want),
             halves_equal=bool(torch.equal(y, y_one)),
@@ -83,6 +93,7 @@ def test_fused_row_parallel_ffn_two_ranks():
     for r in range(world):
         assert out[r]["status"] == 0
         assert out[r]["halves_equal"]          # same slabs summed in the same order: same bits
+        assert out[r]["flags_equal"]           # ... whichever barrier separates the two kernels
         assert out[r]["vs_oracle"] <= 2e-2, out[r]
         # one rounding of the sum instead of one per partial and one for the residual
         assert out[r]["vs_nccl"] <= 2e-2, out[r]

@@ -1258,3 +1258,39 @@ def test_calls_are_cuda_graph_capturable(ops):
             assert torch.equal(replayed, out)
         else:
             torch.testing.assert_close(replayed.float(), out.float(), rtol=2 ** -6, atol=1e-3)
+
+
+def test_peer_flag_barrier_arrivals_and_time_limit(ops):
+    """``dpk_peer_barrier`` on one GPU with the peers' arrivals written by hand: it returns as
+    soon as every slot has reached the epoch, and when a peer never arrives it gives up after the
+    time limit with a status code -- the kernel returns, the context stays usable.  (Between real
+    ranks it is exercised by the two-GPU test and by the benchmark.)"""
+    import ctypes as C
+    import time
+
+    from dpk_b200 import _native
+
+    lib = _native.load()
+    st = torch.cuda.current_stream().cuda_stream
+    mine = torch.zeros(8, dtype=torch.int32, device="cuda")       # this rank's slots (rank 0 of 2)
+    theirs = torch.zeros(8, dtype=torch.int32, device="cuda")     # stands in for rank 1's slots
+    table = (C.c_void_p * 2)(mine.data_ptr(), theirs.data_ptr())
+    # epoch 1: rank 1's arrival is already there
+    mine[1] = 1
+    _native.check(lib.dpk_peer_barrier(table, mine.data_ptr(), 2, 0, 1, 200, st))
+    assert ops.device_status() == 0
+    assert mine.tolist()[:2] == [1, 1] and theirs.tolist()[0] == 1   # published to itself and to the peer
+    # epoch 2: nobody writes slot 1 -> the wait runs out
+    t0 = time.perf_counter()
+    _native.check(lib.dpk_peer_barrier(table, mine.data_ptr(), 2, 0, 2, 50, st))
+    status = ops.device_status()                                   # synchronises and clears the word
+    assert status == 8107, status
+    assert 0.03 < time.perf_counter() - t0 < 2.0
+    # a peer that is one barrier AHEAD counts as arrived
+    mine[1] = 4
+    _native.check(lib.dpk_peer_barrier(table, mine.data_ptr(), 2, 0, 3, 200, st))
+    assert ops.device_status() == 0
+    assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0   # the context is fine
+    # a world of one: no peers to wait for
+    _native.check(lib.dpk_peer_barrier((C.c_void_p * 1)(mine.data_ptr()), mine.data_ptr(), 1, 0, 9, 50, st))
+    assert ops.device_status() == 0 and mine.tolist()[0] == 9
