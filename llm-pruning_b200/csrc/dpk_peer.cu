@@ -82,9 +82,8 @@ __global__ void __launch_bounds__(256) reduce_gather_kernel(const ReduceGatherPa
 // Barrier between the ranks of one node through flags in peer-mapped memory.  Every rank owns
 // an array of `world` 32-bit slots; slot s of rank o's array is written only by rank s.  Thread j
 // of the single block publishes this rank's arrival to rank j (a system-scope release store of
-// the epoch number into slot `rank` of j's array: everything this rank wrote to peer memory
-// before the kernel -- earlier kernels of the same stream included -- is visible to whoever
-// observes the store) and then waits until slot j of its OWN array has reached the epoch.  The
+// the epoch number into slot `rank` of j's array, after the peer stores of the kernels before
+// this one in the stream) and then waits until slot j of its OWN array has reached the epoch.  The
 // wait is bounded: after `limit_cycles` it records a status code and the kernel returns, so the
 // context stays usable; the caller must treat the step's result as invalid then.  Epochs only
 // grow, so a rank that is one barrier ahead cannot be mistaken for one that has arrived at this
@@ -103,19 +102,19 @@ __global__ void __launch_bounds__(32) peer_barrier_table_kernel(const PeerFlagTa
     __threadfence_system();
     uint32_t* remote = peer_flags.p[j] + rank;
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
-    const uint32_t* mine = my_flags + j;
+    // poll with plain (relaxed, uncached) loads and fence once at the end
+    const volatile uint32_t* mine = my_flags + j;
     const long long t0 = clock64();
-    uint32_t seen;
     while (true) {
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        const uint32_t seen = *mine;
         if (static_cast<int32_t>(seen - epoch) >= 0) break;
         if (clock64() - t0 > limit_cycles) {
             atomicCAS(status, 0, 1000 * DPK_KERNEL_ID + DPK_DEV_TIMEOUT_PEER);
             break;
         }
-        __nanosleep(200);
+        __nanosleep(1000);
     }
-    __threadfence_system();
+    __threadfence_system();       // what the peers wrote before their arrival is visible after this
 }
 
 }  // namespace dpk

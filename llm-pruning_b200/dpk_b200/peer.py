@@ -10,7 +10,9 @@ residual) and stores the finished rows into every rank's output.  Between the tw
 and after the second, the ranks meet at a barrier ordered on the stream: a one-element NCCL
 all-reduce (``barrier_mode = "nccl"``, the default) or ``dpk_peer_barrier``, one small kernel
 per rank that publishes an arrival flag in every peer's memory and waits, with a time limit,
-for the peers' flags (``barrier_mode = "flags"``).
+for the peers' flags (``barrier_mode = "flags"``; same results, but measured slower and less
+steady than the NCCL barrier on two GPUs -- 12.9-14.3 against 11.5-11.7 ms per step of the
+70B-shaped layer -- so it is not the default).
 
 Buffers come from the C library (``dpk_peer_alloc``) and are mapped into the peers with
 CUDA IPC; the 64-byte handles travel through ``torch.distributed``.
