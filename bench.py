@@ -533,6 +533,8 @@ def main():
     ap.add_argument("--mn-gather", type=int, default=-1, choices=[-1, 0, 1],
                     help="measurements only: token rows of the output-width GEMM by cp.async (0) or TMA "
                          "tile::gather4 (1); -1 = the library's default")
+    ap.add_argument("--attn-heads", type=int, default=0, choices=[0, 1, 2],
+                    help="measurements only: 2 = the prefill attention kernel with two query heads per CTA")
     ap.add_argument("--one-block", action="store_true",
                     help="profiler captures only: time a single block of --steps steps")
     args = ap.parse_args()
@@ -560,9 +562,11 @@ def main():
     if world > 1:
         dist.barrier()
     from dpk_b200 import ops, workloads as W
-    if args.mn_gather >= 0:
+    if args.mn_gather >= 0 or args.attn_heads:
         from dpk_b200 import _native
-        _native.check(_native.load().dpk_set_gemm_mn_gather(args.mn_gather))
+        if args.mn_gather >= 0:
+            _native.check(_native.load().dpk_set_gemm_mn_gather(args.mn_gather))
+        _native.check(_native.load().dpk_set_attn_prefill_heads(args.attn_heads))
 
     # ---- sub-records of the other configurations (single GPU), before the long loops of the
     # layer heat the GPU into its power cap: these are sub-millisecond kernels, timed as a burst
@@ -790,39 +794,50 @@ def main():
     # ---- the same layer without routing (cuBLAS, SDPA, NCCL all-reduce), same sharding -----
     dense = None
     if not args.skip_dense:
-        wq, wk, wv, wo = layer.wq, layer.wk, layer.wv, layer.wo
+        wo = layer.wo
         wg, wu, wd = layer.ffn.wg, layer.ffn.wu, layer.ffn.wd
         n1, n2 = fe["n1"], fe["n2"]
         D, hq_l, hk_l = shape.head_dim, layer.Hq, layer.Hk
         sdpa = torch.nn.functional.scaled_dot_product_attention
 
-        def rot(t):
-            half = D // 2
-            return t * cos[None, :, None, :] + torch.cat((-t[..., half:], t[..., :half]), -1) * sin[None, :, None, :]
+        wqkv = layer.wqkv                       # [Wq; Wk; Wv] stacked: one library GEMM
+        qd, kd = hq_l * D, hk_l * D
 
         def dense_step():
+            # the glue is as lean as the routed layer's: one stacked q/k/v GEMM, this library's
+            # rotary kernel in place on the slices, residual adds inside the GEMMs (addmm) where
+            # no all-reduce comes between
             xf = x[0]
             xn = torch.nn.functional.rms_norm(xf, (H,), n1, shape.eps)
-            q = rot((xn @ wq.T).view(1, T, hq_l, D)).transpose(1, 2)
-            k = rot((xn @ wk.T).view(1, T, hk_l, D)).transpose(1, 2)
-            v = (xn @ wv.T).view(1, T, hk_l, D).transpose(1, 2)
-            a = sdpa(q, k, v, is_causal=True, enable_gqa=True).transpose(1, 2).reshape(T, hq_l * D)
-            o = a @ wo.T
+            qkv = (xn @ wqkv.T).view(1, T, qd + 2 * kd)
+            q = qkv[..., :qd].view(1, T, hq_l, D)
+            k = qkv[..., qd:qd + kd].view(1, T, hk_l, D)
+            v = qkv[..., qd + kd:].view(1, T, hk_l, D)
+            ops.rope_append(q, k, None, cos, sin)
+            a = sdpa(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True,
+                     enable_gqa=True).transpose(1, 2).reshape(T, hq_l * D)
             if world > 1:
+                o = a @ wo.T
                 dist.all_reduce(o)
-            x1 = xf + o
+                x1 = xf + o
+            else:
+                x1 = torch.addmm(xf, a, wo.T)
             x1n = torch.nn.functional.rms_norm(x1, (H,), n2, shape.eps)
-            yy = (torch.nn.functional.silu(x1n @ wg.T) * (x1n @ wu.T)) @ wd.T
+            hmid = torch.nn.functional.silu(x1n @ wg.T) * (x1n @ wu.T)
             if world > 1:
+                yy = hmid @ wd.T
                 dist.all_reduce(yy)
-            return x1 + yy
+                return x1 + yy
+            return torch.addmm(x1, hmid, wd.T)
 
         dblocks = timed_blocks(dense_step, args.steps, 3, world, device, seconds=1.0, min_blocks=3,
                                max_blocks=10)
         dms = statistics.median(dblocks)
         dense = {"value": T / (dms * 1e-3), "unit": UNIT, "ms_per_step": dms,
-                 "what": "the same layer with every group kept: rms_norm, torch.matmul (cuBLAS bf16), "
-                         "SDPA causal, silu*mul" + (", NCCL all-reduce of both partial sums" if world > 1 else "")}
+                 "what": "the same layer with every group kept: rms_norm, one stacked q/k/v GEMM and the other "
+                         "projections by cuBLAS bf16 (residual adds inside addmm), this library's rotary "
+                         "kernel, SDPA causal, silu*mul" +
+                         (", NCCL all-reduce of both partial sums" if world > 1 else "")}
 
     if rank != 0:
         if world > 1:
