@@ -318,7 +318,15 @@ int dpk_ffn_swiglu_small(const void* x, const void* Wg, const void* Wu, const vo
  * bytes, logits optional fp32 [M,NG,2].  R <= 16, H a multiple of 32 and at most ~14000.
  * round_like_module != 0 rounds c and the logits to `dtype` as a module running in that
  * dtype does; 0 keeps fp32.  x is read from device memory once.
+ * Where H splits into 1, 2, 4 or 8 slices of at most 2048 columns (multiples of 32) a cluster
+ * of that many CTAs works on 16 rows at a time, each CTA keeping its slice of w_down in shared
+ * memory and streaming its columns of the rows through a ring of bulk copies; the partial
+ * sums meet through distributed shared memory.  Other widths (up to ~14000 columns) take the
+ * one-CTA-per-tile kernel, which re-reads w_down from L2 for every 8 rows.
+ * dpk_set_router_norm_cluster(0) forces the latter everywhere (a measurement switch, process
+ * wide; 1 = default).  No reference counterpart for the switch.
  */
+int dpk_set_router_norm_cluster(int on);
 int dpk_router_norm(const void* x, int64_t ldx, const void* gamma, float eps, const void* w_down,
                     const void* b_down, const void* w_route, const void* b_route, void* xn,
                     int64_t ldxn, uint8_t* execute, float* logits, int64_t M, int H, int R, int NG,

@@ -287,8 +287,11 @@ def main(argv=None):
                     help="gemm_mn / ffn: token rows by cp.async (0) or TMA tile::gather4 (1); -1 = the default")
     ap.add_argument("--heads-per-cta", type=int, default=0, choices=[0, 1, 2],
                     help="attention_prefill: 2 = the two-heads-per-CTA kernel, 0/1 = one head per CTA")
+    ap.add_argument("--router-cluster", type=int, default=1, choices=[0, 1],
+                    help="router_norm: 1 = column-split cluster kernel where the width allows, 0 = one CTA per tile")
     args = ap.parse_args(argv)
     assert torch.cuda.is_available(), "dpk_b200.perf needs a CUDA device"
+    _native.check(_native.load().dpk_set_router_norm_cluster(args.router_cluster))
     _native.check(_native.load().dpk_set_attn_prefill_heads(args.heads_per_cta))
     if args.gather4 >= 0:
         _native.check(_native.load().dpk_set_gemm_mn_gather(args.gather4))
