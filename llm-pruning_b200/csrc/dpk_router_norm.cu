@@ -314,28 +314,34 @@ __global__ void __launch_bounds__(kRnThreads, 1) router_norm_kernel(const Router
 // ---------------------------------------------------------------------------------------------
 // Column-split variant: a cluster of C CTAs shares a 16-row tile, each CTA owning H / C columns.
 //
-// What bounds the kernel above is not arithmetic.  Beside 130-220 KB of row buffers an SM has a
-// few KB of L1 left, and per-thread global stores wait there until L2 has taken them, so the
-// write-out trickles; every phase sits behind a CTA-wide barrier; and the first-stage weights
-// (16 x H halves) stream from L2 again for every 8 rows.  Here
+// What bounds the kernel above is not memory.  One CTA per SM at H = 8192, every phase behind a
+// CTA-wide barrier, the first-stage weights (16 x H halves) streamed from L2 again for every
+// 8 rows, and a second stage whose scalar arithmetic sits on a few warps: the loads run out
+// while the arithmetic runs, and the other way round.  Here
 //   * the CTA is split into two groups of eight warps that work on different tiles at the same
 //     time: the CONTRACTING warps (first stage, exchange, second stage, decisions) and the
 //     NORMALISING warps (scaling in place in shared memory; their first warp also issues all
 //     bulk copies).  Row slices go through a ring of 3-4 stages: one being normalised and
 //     drained, one being contracted, the rest in flight;
-//   * the normalised rows leave through bulk stores from shared memory, which do not pass L1;
+//   * the normalised rows leave through bulk stores from shared memory;
 //   * a contracting thread keeps its fragments of the [16 x H/C] weight slice in registers for
 //     the whole launch (64 registers), so the slice occupies no shared memory or bandwidth;
 //   * both row halves of the m16n8k16 tile carry tokens;
-//   * the C partial contractions and sums of squares of a row meet through distributed shared
-//     memory without a cluster barrier: rank q finishes the contraction of rows q*16/C ..., so
-//     every CTA pushes those rows' partials, and all 16 partial sums of squares, into rank q's
+//   * the C partial contractions and sums of squares of a tile meet through distributed shared
+//     memory without a cluster barrier: every CTA pushes its 16 x 17 partials into every rank's
 //     receive slot with st.async, which counts the bytes on an mbarrier of the receiver; the
-//     slots are summed in rank order, so all ranks normalise with the same scale;
-//   * the second stage [rows x 16] x [16 x 2*NG] is a handful of MMAs spread over the warps
-//     (when the contraction is rounded to the tensor dtype, as a module in that dtype does; the
-//     fp32 variant keeps scalar arithmetic); the decisions are collected in shared memory and
-//     leave as one coalesced store.
+//     slots are summed in rank order, so all ranks hold the same contraction and normalise with
+//     the same scales;
+//   * the second stage [16 x 16] x [16 x 2*NG] is split by groups: rank q computes the logits
+//     and decisions of groups q*NG/C ... for all 16 rows, a few full MMAs per warp (when the
+//     contraction is rounded to the tensor dtype, as a module in that dtype does; the fp32
+//     variant keeps scalar arithmetic), with its share of the second-stage weights staged in
+//     shared memory; the decisions are collected there too and leave as 4-byte stores.
+// Measured on the 70B-shaped layer's router (M = 16384, H = 8192, 224 groups): every variant that
+// kept one CTA-wide sequence of phases took 0.16-0.20 ms whatever the data path; with the
+// second stage split by rows instead of groups (a quarter-filled MMA tile per rank, four times
+// the MMAs and their epilogues) 0.158 ms; this layout 0.127 ms.  The same loads, barriers and
+// stores without any arithmetic take 0.099 ms.
 // Two receive slots alternate.  A CTA can only push for tile i+2 after it has seen every peer's
 // push for tile i+1, which a peer issues after reading its slot of tile i, so a slot is never
 // overwritten before it has been read.  Every wait is bounded; a group that gives up raises the
@@ -349,8 +355,8 @@ constexpr int kRcMaxStages = 4;
 constexpr int kRcMaxSlice = 2048;                     // columns per CTA
 constexpr int kRcKPerWarp = kRcMaxSlice / 32 / kRcGWarps;   // 32-wide k-blocks of a contracting warp: 8
 constexpr int kRcMaxCluster = 8;
-constexpr int kRcSlot = kRcRows * kRnRank + kRcRows * kRcMaxCluster;   // floats a CTA receives per tile, at most
-constexpr int kRcExBytes = 4096;                      // decisions of one tile collected in shared memory, at most
+constexpr int kRcPart = kRcRows * (kRnRank + 1);      // partials of one tile: 16 x 16 contraction + 16 sums of squares
+constexpr int kRcExBytes = 2048;                      // decisions of one tile collected in shared memory, at most
 
 __device__ __forceinline__ uint32_t cluster_nctarank()
 {
@@ -482,23 +488,24 @@ router_norm_cluster_kernel(const RouterNormParams p, const int hc, const int sta
     uint8_t* ring = rn_smem;                                            // [stages][16][pitch]
     float* cpart = reinterpret_cast<float*>(ring + size_t(stages) * kRcRows * pitch);   // [warps][rows][16]
     float* sspart = cpart + kRcGWarps * kRcRows * kRnRank;              // [warps][rows]
-    float* slot = sspart + kRcGWarps * kRcRows;                         // [2][kRcSlot], written by the cluster
-    float* cfin = slot + 2 * kRcSlot;                                   // [rows of this rank][16]
+    float* slot = sspart + kRcGWarps * kRcRows;                         // [2][csize][kRcPart], written by the cluster
+    float* cfin = slot + 2 * cluster_nctarank() * kRcPart;              // [rows][16]
     float* rs = cfin + kRcRows * kRnRank;                               // [kRcMaxStages][rows]
     uint8_t* exbuf = reinterpret_cast<uint8_t*>(rs + kRcMaxStages * kRcRows);     // [kRcExBytes]
     uint64_t* full = reinterpret_cast<uint64_t*>(exbuf + kRcExBytes);   // [kRcMaxStages] rows landed
     uint64_t* ready = full + kRcMaxStages;                              // [kRcMaxStages] scales of the stage written
     uint64_t* xbar = ready + kRcMaxStages;                              // [2] partials of a tile received
     volatile int* abort_flag = reinterpret_cast<volatile int*>(xbar + 2);
-    // second-stage weights [2*NG][16] halves, zero beyond the rank, then the biases [2*NG] halves
-    // (only when wr_staged: they fit behind the rest)
+    // this rank's groups of the second stage: weights [2*ng][16] halves, zero beyond the router's
+    // rank, then the biases [2*ng] halves (only when wr_staged: they fit behind the rest)
     uint8_t* wr = reinterpret_cast<uint8_t*>(xbar + 2) + 16;
-    uint8_t* wrb = wr + size_t(2 * p.NG) * kRnRank * 2;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = cluster_ctarank(), csize = cluster_nctarank();
-    const int rpr = kRcRows / static_cast<int>(csize);       // rows whose contraction this rank finishes
-    const int per_src = rpr * kRnRank + kRcRows;             // floats received from one rank per tile
+    // the groups whose logits and decisions this rank computes, for all 16 rows of a tile
+    const int g0 = static_cast<int>(int64_t(p.NG) * rank / csize);
+    const int ng = static_cast<int>(int64_t(p.NG) * (rank + 1) / csize) - g0;
+    uint8_t* wrb = wr + size_t(2 * ng) * kRnRank * 2;
     const int64_t col0 = int64_t(rank) * hc;
     const int64_t ntiles = (p.M + kRcRows - 1) / kRcRows;
     const int64_t first = cluster_id_x(), step = cluster_count_x();
@@ -519,14 +526,14 @@ router_norm_cluster_kernel(const RouterNormParams p, const int hc, const int sta
     }
     if (wr_staged) {
         uint16_t* w16 = reinterpret_cast<uint16_t*>(wr);
-        const uint16_t* src = reinterpret_cast<const uint16_t*>(p.w_route);
-        for (int i = tid; i < 2 * p.NG * kRnRank; i += kRcThreads) {
+        const uint16_t* src = reinterpret_cast<const uint16_t*>(p.w_route) + int64_t(2 * g0) * p.R;
+        for (int i = tid; i < 2 * ng * kRnRank; i += kRcThreads) {
             const int n = i / kRnRank, k = i % kRnRank;
             w16[i] = k < p.R ? src[int64_t(n) * p.R + k] : uint16_t(0);
         }
         uint16_t* b16 = reinterpret_cast<uint16_t*>(wrb);
-        for (int i = tid; i < 2 * p.NG; i += kRcThreads)
-            b16[i] = p.b_route ? reinterpret_cast<const uint16_t*>(p.b_route)[i] : uint16_t(0);
+        for (int i = tid; i < 2 * ng; i += kRcThreads)
+            b16[i] = p.b_route ? reinterpret_cast<const uint16_t*>(p.b_route)[2 * g0 + i] : uint16_t(0);
     }
     __syncthreads();
     cluster_sync_all();       // every CTA's barriers exist before a peer pushes to them
@@ -537,10 +544,11 @@ router_norm_cluster_kernel(const RouterNormParams p, const int hc, const int sta
         const int fq = lane & 3;
         const int fk = fq * 8;                // this thread's 8 consecutive k inside a 32-wide block
         const int kblocks = hc / 32;
-        const uint32_t xbytes = csize * static_cast<uint32_t>(per_src) * 4u;
-        const int ntile8 = (2 * p.NG + 7) / 8;          // 8-column tiles of the second stage
-        const int exrow = p.NG;                          // bytes of decisions per row
-        const bool ex_staged = rpr * exrow <= kRcExBytes && exrow % 4 == 0 &&
+        const uint32_t xbytes = csize * static_cast<uint32_t>(kRcPart) * 4u;
+        const int ntile8 = (2 * ng + 7) / 8;            // 8-column tiles of this rank's share of the second stage
+        // this rank's decisions of a tile are collected in shared memory and leave as 4-byte stores
+        // where every row's run of ng bytes starts and ends on a 4-byte boundary
+        const bool ex_staged = kRcRows * ng <= kRcExBytes && ng % 4 == 0 && g0 % 4 == 0 && p.NG % 4 == 0 &&
                                (reinterpret_cast<uintptr_t>(p.execute) & 3u) == 0;
 
         // this thread's fragments of the weight slice, for the whole launch
@@ -620,111 +628,86 @@ router_norm_cluster_kernel(const RouterNormParams p, const int hc, const int sta
             }
             group_sync(1);
 
-            // ---- this CTA's partials go to the ranks that finish them -------------------------------
-            for (int i = tid; i < kRcRows * kRnRank + kRcRows * static_cast<int>(csize); i += kRcGroup) {
+            // ---- this CTA's partials go to every rank of the cluster ------------------------------------
+            for (int e = tid; e < kRcPart; e += kRcGroup) {
                 float v = 0.f;
-                uint32_t dst_rank;
-                int off;
-                if (i < kRcRows * kRnRank) {
-                    const int r = i / kRnRank, j = i % kRnRank;
+                if (e < kRcRows * kRnRank) {
 #pragma unroll
-                    for (int w = 0; w < kRcGWarps; ++w) v += cpart[w * kRcRows * kRnRank + i];
-                    dst_rank = static_cast<uint32_t>(r / rpr);
-                    off = (r % rpr) * kRnRank + j;
+                    for (int w = 0; w < kRcGWarps; ++w) v += cpart[w * kRcRows * kRnRank + e];
                 } else {
-                    const int k = i - kRcRows * kRnRank, r = k % kRcRows;
 #pragma unroll
-                    for (int w = 0; w < kRcGWarps; ++w) v += sspart[w * kRcRows + r];
-                    dst_rank = static_cast<uint32_t>(k / kRcRows);
-                    off = rpr * kRnRank + r;
+                    for (int w = 0; w < kRcGWarps; ++w) v += sspart[w * kRcRows + e - kRcRows * kRnRank];
                 }
-                const float* own = slot + par * kRcSlot + static_cast<int>(rank) * per_src + off;
-                st_async_f32(cluster_addr(own, dst_rank), v, cluster_addr(&xbar[par], dst_rank));
+                const float* own = slot + (par * static_cast<int>(csize) + static_cast<int>(rank)) * kRcPart + e;
+                for (uint32_t dst = 0; dst < csize; ++dst)
+                    st_async_f32(cluster_addr(own, dst), v, cluster_addr(&xbar[par], dst));
             }
             if (!group_all(1, mbar_wait(&xbar[par], xphase, abort_flag, p.status, DPK_DEV_TIMEOUT_PEER))) break;
-            for (int i = tid; i < per_src; i += kRcGroup) {       // up to 272 values
-                const float* src = slot + par * kRcSlot + i;
+            for (int e = tid; e < kRcPart; e += kRcGroup) {
+                const float* src = slot + par * static_cast<int>(csize) * kRcPart + e;
                 float v = 0.f;
-                for (uint32_t c = 0; c < csize; ++c) v += src[c * per_src];
-                if (i < rpr * kRnRank) {
-                    const int j = i % kRnRank;
+                for (uint32_t c = 0; c < csize; ++c) v += src[c * kRcPart];
+                if (e < kRcRows * kRnRank) {
+                    const int j = e % kRnRank;
                     if (j < p.R && p.b_down) v += half_at<kBf16>(p.b_down, j);
                     if (p.round_like_module) v = round_half<kBf16>(v);
-                    cfin[i] = j < p.R ? v : 0.f;
+                    cfin[e] = j < p.R ? v : 0.f;
                 } else {
-                    rs[s * kRcRows + i - rpr * kRnRank] = rsqrtf(v / static_cast<float>(p.H) + p.eps);
+                    rs[s * kRcRows + e - kRcRows * kRnRank] = rsqrtf(v / static_cast<float>(p.H) + p.eps);
                 }
             }
             group_sync(1);
             if (tid == 0) mbar_arrive(&ready[s]);      // the normalising warps may take the stage
 
-            // ---- second stage and the decision for this rank's rows ----------------------------------
-            const int64_t myrow0 = row0 + int64_t(rank) * rpr;
-            int64_t left = p.M - myrow0;
-            const int myrows = left <= 0 ? 0 : (left < rpr ? static_cast<int>(left) : rpr);
+            // ---- second stage and the decisions: all 16 rows, this rank's groups ------------------------
+            const int nrows = rows_of(tile);
+            auto record = [&](int r, int gl, float la, float lb) {      // row of the tile, group of this rank
+                const uint8_t e = la >= lb ? 1 : 0;
+                if (ex_staged)
+                    exbuf[r * ng + gl] = e;
+                else
+                    p.execute[(row0 + r) * p.NG + g0 + gl] = e;
+                if (p.logits)
+                    *reinterpret_cast<float2*>(p.logits + ((row0 + r) * p.NG + g0 + gl) * 2) = make_float2(la, lb);
+            };
             if (p.round_like_module) {
-                // A = the finished contraction (exact in the tensor dtype), rows beyond rpr zero
-                uint32_t a0 = 0u, a1 = 0u, a2 = 0u, a3 = 0u;
-                if (frow < rpr) {
-                    const float* c = cfin + frow * kRnRank + fq * 2;
-                    a0 = pack_half2<kBf16>(c[0], c[1]);
-                    a2 = pack_half2<kBf16>(c[8], c[9]);
-                }
-                if (frow + 8 < rpr) {
-                    const float* c = cfin + (frow + 8) * kRnRank + fq * 2;
-                    a1 = pack_half2<kBf16>(c[0], c[1]);
-                    a3 = pack_half2<kBf16>(c[8], c[9]);
-                }
-                // the logits of one 8-column tile: add the biases, round, compare, record
-                auto decide = [&](int nt, const float (&l)[4], float ba, float bb) {
-                    const int g = nt * 4 + fq;                       // columns 2g, 2g+1 are this thread's
-                    if (g < p.NG) {
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const int rr = frow + 8 * h;
-                            if (rr < myrows) {
-                                const float la = round_half<kBf16>(l[2 * h] + ba);
-                                const float lb = round_half<kBf16>(l[2 * h + 1] + bb);
-                                const uint8_t e = la >= lb ? 1 : 0;
-                                if (ex_staged)
-                                    exbuf[rr * exrow + g] = e;
-                                else
-                                    p.execute[(myrow0 + rr) * p.NG + g] = e;
-                                if (p.logits)
-                                    *reinterpret_cast<float2*>(p.logits + ((myrow0 + rr) * p.NG + g) * 2) =
-                                        make_float2(la, lb);
-                            }
-                        }
-                    }
-                };
+                // A = the finished contraction of the 16 rows (exact in the tensor dtype)
+                const float* ca = cfin + frow * kRnRank + fq * 2;
+                const float* cb = ca + 8 * kRnRank;
+                const uint32_t a0 = pack_half2<kBf16>(ca[0], ca[1]), a2 = pack_half2<kBf16>(ca[8], ca[9]);
+                const uint32_t a1 = pack_half2<kBf16>(cb[0], cb[1]), a3 = pack_half2<kBf16>(cb[8], cb[9]);
                 for (int nt = warp; nt < ntile8; nt += kRcGWarps) {
-                    const int nb = nt * 8 + frow, g = nt * 4 + fq;
-                    const bool nb_ok = nb < 2 * p.NG, g_ok = g < p.NG;
+                    const int nb = nt * 8 + frow, gl = nt * 4 + fq;      // columns 2 gl, 2 gl + 1 are this thread's
+                    const bool nb_ok = nb < 2 * ng, g_ok = gl < ng;
                     uint32_t b0, b1;
                     float ba = 0.f, bb = 0.f;
                     if (wr_staged) {
                         const uint32_t* wrow = reinterpret_cast<const uint32_t*>(wr + size_t(nb) * kRnRank * 2);
                         b0 = nb_ok ? wrow[fq] : 0u;
                         b1 = nb_ok ? wrow[fq + 4] : 0u;
-                        if (g_ok) unpack_half2<kBf16>(reinterpret_cast<const uint32_t*>(wrb)[g], ba, bb);
+                        if (g_ok) unpack_half2<kBf16>(reinterpret_cast<const uint32_t*>(wrb)[gl], ba, bb);
                     } else {
-                        b0 = route_pair<kBf16>(p, nb, fq * 2, nb_ok);
-                        b1 = route_pair<kBf16>(p, nb, fq * 2 + 8, nb_ok);
+                        b0 = route_pair<kBf16>(p, 2 * g0 + nb, fq * 2, nb_ok);
+                        b1 = route_pair<kBf16>(p, 2 * g0 + nb, fq * 2 + 8, nb_ok);
                         if (g_ok && p.b_route) {
-                            ba = half_at<kBf16>(p.b_route, 2 * g);
-                            bb = half_at<kBf16>(p.b_route, 2 * g + 1);
+                            ba = half_at<kBf16>(p.b_route, 2 * (g0 + gl));
+                            bb = half_at<kBf16>(p.b_route, 2 * (g0 + gl) + 1);
                         }
                     }
                     float l[4] = {0.f, 0.f, 0.f, 0.f};
                     rc_mma<kBf16>(l, a0, a1, a2, a3, b0, b1);
-                    decide(nt, l, ba, bb);
+                    if (g_ok) {
+                        if (frow < nrows) record(frow, gl, round_half<kBf16>(l[0] + ba), round_half<kBf16>(l[1] + bb));
+                        if (frow + 8 < nrows)
+                            record(frow + 8, gl, round_half<kBf16>(l[2] + ba), round_half<kBf16>(l[3] + bb));
+                    }
                 }
             } else {
-                for (int item = tid; item < myrows * p.NG; item += kRcGroup) {
-                    const int rr = item / p.NG, g = item % p.NG;
+                for (int item = tid; item < nrows * ng; item += kRcGroup) {
+                    const int r = item / ng, gl = item % ng, g = g0 + gl;
                     float la = 0.f, lb = 0.f;
                     for (int j = 0; j < p.R; ++j) {
-                        const float c = cfin[rr * kRnRank + j];
+                        const float c = cfin[r * kRnRank + j];
                         la = fmaf(c, half_at<kBf16>(p.w_route, int64_t(2 * g) * p.R + j), la);
                         lb = fmaf(c, half_at<kBf16>(p.w_route, int64_t(2 * g + 1) * p.R + j), lb);
                     }
@@ -732,21 +715,17 @@ router_norm_cluster_kernel(const RouterNormParams p, const int hc, const int sta
                         la += half_at<kBf16>(p.b_route, 2 * g);
                         lb += half_at<kBf16>(p.b_route, 2 * g + 1);
                     }
-                    const uint8_t e = la >= lb ? 1 : 0;
-                    if (ex_staged)
-                        exbuf[rr * exrow + g] = e;
-                    else
-                        p.execute[(myrow0 + rr) * p.NG + g] = e;
-                    if (p.logits)
-                        *reinterpret_cast<float2*>(p.logits + ((myrow0 + rr) * p.NG + g) * 2) = make_float2(la, lb);
+                    record(r, gl, la, lb);
                 }
             }
             if (ex_staged) {
-                // this rank's rows of the decisions are one contiguous, 4-byte aligned range
                 group_sync(1);
-                uint32_t* dst = reinterpret_cast<uint32_t*>(p.execute + myrow0 * p.NG);
+                const int wpr = ng / 4;                              // 4-byte words per row
                 const uint32_t* src = reinterpret_cast<const uint32_t*>(exbuf);
-                for (int i = tid; i < myrows * exrow / 4; i += kRcGroup) dst[i] = src[i];
+                for (int i = tid; i < nrows * wpr; i += kRcGroup) {
+                    const int r = i / wpr, w = i % wpr;
+                    reinterpret_cast<uint32_t*>(p.execute + (row0 + r) * p.NG + g0)[w] = src[i];
+                }
                 // the next tile writes exbuf after two more group barriers
             }
         }
@@ -852,27 +831,27 @@ int rn_cluster_size(int H)
     return 0;
 }
 
-size_t rn_cluster_smem(int hc, int stages)
+size_t rn_cluster_smem(int hc, int stages, int csize)
 {
     const size_t pitch = size_t(hc) * 2 + kRnSkew;
     return size_t(stages) * kRcRows * pitch +
-           sizeof(float) * (kRcGWarps * kRcRows * kRnRank + kRcGWarps * kRcRows + 2 * kRcSlot +
+           sizeof(float) * (kRcGWarps * kRcRows * kRnRank + kRcGWarps * kRcRows + 2 * csize * kRcPart +
                             kRcRows * kRnRank + kRcMaxStages * kRcRows) +
            kRcExBytes + sizeof(uint64_t) * (2 * kRcMaxStages + 2) + 16;
 }
 
-// second-stage weights and biases staged in shared memory, as halves
-size_t rn_route_smem(int NG) { return size_t(2 * NG) * (kRnRank + 1) * 2 + 16; }
+// a rank's share of the second-stage weights and biases staged in shared memory, as halves
+size_t rn_route_smem(int NG, int csize) { return size_t(2 * ((NG + csize - 1) / csize)) * (kRnRank + 1) * 2 + 16; }
 
 template <bool kBf16>
 int launch_router_norm_cluster(const RouterNormParams& p, int csize, cudaStream_t s)
 {
     const int hc = p.H / csize;
     int stages = kRcMaxStages;
-    while (stages > 3 && rn_cluster_smem(hc, stages) > 227 * 1024) --stages;
+    while (stages > 3 && rn_cluster_smem(hc, stages, csize) > 227 * 1024) --stages;
     // the second stage's operands go behind the ring if they fit (else they come from L2 per tile)
-    const int wr_staged = rn_cluster_smem(hc, stages) + rn_route_smem(p.NG) <= 227 * 1024 ? 1 : 0;
-    const size_t smem = rn_cluster_smem(hc, stages) + (wr_staged ? rn_route_smem(p.NG) : 0);
+    const int wr_staged = rn_cluster_smem(hc, stages, csize) + rn_route_smem(p.NG, csize) <= 227 * 1024 ? 1 : 0;
+    const size_t smem = rn_cluster_smem(hc, stages, csize) + (wr_staged ? rn_route_smem(p.NG, csize) : 0);
     DPK_CUDA(cudaFuncSetAttribute(router_norm_cluster_kernel<kBf16>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaLaunchAttribute attr[1];
@@ -968,7 +947,7 @@ extern "C" int dpk_router_norm(const void* x, int64_t ldx, const void* gamma, fl
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int csize = g_rn_cluster ? rn_cluster_size(H) : 0;
-    if (csize > 0 && rn_cluster_smem(H / csize, 3) <= 227 * 1024)
+    if (csize > 0 && rn_cluster_smem(H / csize, 3, csize) <= 227 * 1024)
         return dtype == DPK_BF16 ? launch_router_norm_cluster<true>(p, csize, s)
                                  : launch_router_norm_cluster<false>(p, csize, s);
 
