@@ -564,6 +564,9 @@ router_norm_cluster_kernel(const RouterNormParams p, const int hc, const int sta
                     wf1[i] = __ldg(reinterpret_cast<const uint4*>(p.w_down + (int64_t(frow + 8) * p.H + k) * 2));
             }
         }
+        // first-stage bias of the column this thread finishes (a global load inside the loop would
+        // put a round trip to L2 on every tile's critical path)
+        const float bias_down = (tid % kRnRank < p.R && p.b_down) ? half_at<kBf16>(p.b_down, tid % kRnRank) : 0.f;
         int64_t it = 0;
         for (int64_t tile = first; tile < ntiles; tile += step, ++it) {
             const int s = static_cast<int>(it % stages);
@@ -648,8 +651,8 @@ router_norm_cluster_kernel(const RouterNormParams p, const int hc, const int sta
                 float v = 0.f;
                 for (uint32_t c = 0; c < csize; ++c) v += src[c * kRcPart];
                 if (e < kRcRows * kRnRank) {
-                    const int j = e % kRnRank;
-                    if (j < p.R && p.b_down) v += half_at<kBf16>(p.b_down, j);
+                    const int j = e % kRnRank;          // == tid % kRnRank
+                    v += bias_down;
                     if (p.round_like_module) v = round_half<kBf16>(v);
                     cfin[e] = j < p.R ? v : 0.f;
                 } else {
