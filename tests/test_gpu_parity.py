@@ -763,7 +763,18 @@ def test_row_parallel_sum_emulated_ranks(ops, world, M, N, Kl, NGl):
             assert torch.equal(outs[r], outs[0])
 
 
-def test_router_norm_golden_fixture(ops):
+@pytest.fixture(params=[1, 0], ids=["cluster", "one_cta_per_tile"])
+def router_kernel(request):
+    """Both router + norm kernels: the column-split cluster kernel (default where the width
+    splits) and the one-CTA-per-tile kernel, forced through the library's switch."""
+    from dpk_b200 import _native
+    lib = _native.load()
+    _native.check(lib.dpk_set_router_norm_cluster(request.param))
+    yield request.param
+    _native.check(lib.dpk_set_router_norm_cluster(1))
+
+
+def test_router_norm_golden_fixture(ops, router_kernel):
     """The reference's TokenRouter (bf16 module and fp32 module) and LlamaRMSNorm outputs."""
     z = golden_io.load("router_norm")
     bf = torch.bfloat16
@@ -795,9 +806,14 @@ def test_router_norm_golden_fixture(ops):
                                                    (301, 8192, 224, 16, torch.bfloat16, True),
                                                    (77, 1024, 8, 16, torch.float16, True),
                                                    (64, 512, 300, 8, torch.bfloat16, False),
-                                                   (5, 2048, 1, 3, torch.bfloat16, False)])
-def test_router_norm_against_oracle(ops, M, H, NG, R, dtype, biases):
-    """Ragged last tile, more groups than threads, router ranks below 16, fp16, no biases."""
+                                                   (5, 2048, 1, 3, torch.bfloat16, False),
+                                                   (203, 8192, 8, 16, torch.bfloat16, True),
+                                                   (40, 12288, 64, 16, torch.bfloat16, True),
+                                                   (33, 2080, 10, 5, torch.float16, True)])
+def test_router_norm_against_oracle(ops, router_kernel, M, H, NG, R, dtype, biases):
+    """Ragged last tile, more groups than threads, router ranks below 16, fp16, no biases; clusters
+    of 1, 2, 4 and 8 CTAs (H = 12288 splits eight ways), fewer groups than a rank's share needs
+    for word stores, and a width that does not split (2080), which takes the one-CTA kernel."""
     g = seeded(M + H)
     def rnd(*shape, std=1.0):
         return (torch.randn(*shape, generator=g) * std).to(dtype).float()
