@@ -461,6 +461,22 @@ def _leftpad_arg(Leftpad: Optional[torch.Tensor], B: int, dev) -> Optional[torch
     return lp.to(torch.int64).to(torch.int32).contiguous()   # same 32 bits as uint32
 
 
+def _padded_head_dim(D: int) -> int:
+    """The kernels are built for head sizes 64 and 128.  The reference's attention accepts every
+    multiple of 32 (``include/attention_prefill/v3/sm12x.cuh:88-99``); 32 and 96 run here with
+    zero columns appended to q, k and v (dot products and outputs are unchanged, the softmax
+    scale stays that of the original size) at the price of the padded copies."""
+    if D in (64, 128):
+        return D
+    if D % 32 or D <= 0 or D > 128:
+        raise ValueError(f"head_dim {D} not supported: multiples of 32 up to 128")
+    return 64 if D < 64 else 128
+
+
+def _pad_heads(t: torch.Tensor, Dp: int) -> torch.Tensor:
+    return torch.nn.functional.pad(t, (0, Dp - t.shape[-1]))
+
+
 def attention_prefill(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Mask: torch.Tensor,
                       Leftpad: Optional[torch.Tensor] = None, O: Optional[torch.Tensor] = None,
                       sorted_mask: Optional[torch.Tensor] = None,
@@ -482,6 +498,15 @@ def attention_prefill(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Mask: t
     B, Tq, Hq, D = Q.shape
     _, Tk, Hk, _ = K.shape
     NG = Mask.shape[-1]
+    Dp = _padded_head_dim(D)
+    if Dp != D:
+        Op, meta = attention_prefill(_pad_heads(Q, Dp), _pad_heads(K, Dp), _pad_heads(V, Dp), Mask, Leftpad,
+                                     None, sorted_mask, sorted_indices, D ** -0.5 if scale is None else scale,
+                                     is_causal, estimate_sparsity, kernel_version, arch, autotune, cudagraph)
+        if O is None:
+            return Op[..., :D].contiguous(), meta
+        O.copy_(Op[..., :D])
+        return O, meta
     Qc, q_ts, q_bs = _heads_view(Q)
     Kc, kv_ts, kv_bs = _heads_view(K)
     Vc, v_ts, v_bs = _heads_view(V)
@@ -531,6 +556,15 @@ def attention_decode(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Mask: to
     B, _, Hq, D = Q.shape
     _, Tk, Hk, _ = K.shape
     NG = Mask.shape[-1]
+    Dp = _padded_head_dim(D)
+    if Dp != D:
+        Op, meta = attention_decode(_pad_heads(Q, Dp), _pad_heads(K, Dp), _pad_heads(V, Dp), Mask, Leftpad,
+                                    None, sorted_mask, sorted_indices, D ** -0.5 if scale is None else scale,
+                                    is_causal, estimate_sparsity, kernel_version, arch, autotune, cudagraph)
+        if O is None:
+            return Op[..., :D].contiguous(), meta
+        O.copy_(Op[..., :D])
+        return O, meta
     Qc = Q.contiguous()
     Kc, kv_ts, kv_bs = _heads_view(K)
     Vc, v_ts, v_bs = _heads_view(V)

@@ -383,6 +383,8 @@ def test_prefill_golden(ops):
     (2, 333, 8, 2, 128, 2, torch.bfloat16),
     (1, 1000, 32, 8, 128, 8, torch.bfloat16),     # benchmark head layout
     (1, 257, 8, 8, 64, 4, torch.bfloat16),        # groups spanning 2 KV heads
+    (2, 300, 8, 4, 96, 2, torch.bfloat16),        # head sizes the reference takes beside 64 and 128:
+    (1, 200, 4, 2, 32, 4, torch.float16),         # run with zero columns appended
 ])
 def test_prefill_random(ops, B, T, Hq, Hk, D, NG, dtype):
     g = seeded(T + Hq)
@@ -439,6 +441,8 @@ def test_decode_golden(ops):
     (4, 5000, 32, 8, 128, 8),      # benchmark head layout, several splits
     (2, 1025, 8, 8, 64, 8),
     (3, 700, 16, 4, 128, 2),
+    (2, 900, 8, 4, 96, 4),         # head sizes beside 64 and 128: zero columns appended
+    (1, 130, 4, 4, 32, 2),
 ])
 def test_decode_random(ops, B, Tk, Hq, Hk, D, NG):
     g = seeded(Tk + B)
