@@ -1280,6 +1280,34 @@ def test_calls_are_cuda_graph_capturable(ops):
             torch.testing.assert_close(replayed.float(), out.float(), rtol=2 ** -6, atol=1e-3)
 
 
+@pytest.mark.parametrize("H", [8192, 2080])
+def test_router_norm_is_cuda_graph_capturable(ops, H):
+    """The router + norm call (a cluster launch at H = 8192, a plain launch at a width that does
+    not split) captured into a CUDA graph and replayed on new inputs gives what an eager call
+    gives: both kernels sum in a fixed order."""
+    bf = torch.bfloat16
+    g = seeded(H)
+    M, NG, R = 300, 24, 16
+    x = dev(bf16r(torch.randn(M, H, generator=g)), bf)
+    wd = dev(bf16r(torch.randn(R, H, generator=g) * H ** -0.5), bf)
+    wr = dev(bf16r(torch.randn(2 * NG, R, generator=g) * 0.25), bf)
+    gamma = dev(bf16r(1.0 + 0.1 * torch.randn(H, generator=g)), bf)
+    call = lambda: ops.router_norm(x, wd, None, wr, None, norm_weight=gamma, eps=1e-5)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        call()                                              # warm-up outside the capture
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = call()
+    x.copy_(torch.randn(M, H, device="cuda").to(bf))
+    graph.replay()
+    execute, xn, _ = call()
+    assert torch.equal(captured[0], execute) and torch.equal(captured[1], xn)
+    assert ops.device_status() == 0
+
+
 def test_peer_flag_barrier_arrivals_and_time_limit(ops):
     """``dpk_peer_barrier`` on one GPU with the peers' arrivals written by hand: it returns as
     soon as every slot has reached the epoch, and when a peer never arrives it gives up after the
