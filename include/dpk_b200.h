@@ -195,7 +195,15 @@ int dpk_set_gemm_mn_gather(int mode);
  *   (python/gemm_k/jit.py:368);
  *   workspace: see dpk_gemm_k_workspace_bytes (may be NULL).
  * Requirements: G = K/NG a multiple of 64, N % 8 == 0, 16-byte aligned rows.
+ * Large shapes run on CTA pairs (one tile = 256 tokens x 256 outputs).  Where W is larger
+ * than L2, their tiles are walked in groups of 8 weight chunks with the token windows inside, and the copy-issuing threads of all
+ * CTAs line up at the start of every wave of tiles (a counter per wave in a per-device array,
+ * zeroed on the stream before the launch; a bounded wait that is given up silently), so that
+ * tiles sharing an operand find it in L2: 7.9 GB instead of 24.2 GB of DRAM reads for the
+ * 16384 x 28672 x 8192 down projection.  dpk_set_gemm_k_wave_order(0) restores the plain order
+ * without alignment (process-wide; for measurements and tests; same bits either way).
  */
+int dpk_set_gemm_k_wave_order(int on);
 int dpk_gemm_k(const void* A, int64_t lda, const void* W, int64_t ldw, const uint32_t* row_bits,
                const uint32_t* win_bits, void* D, int64_t ldd, int64_t M, int N, int K, int NG,
                int dtype, const void* residual, int64_t ldr, void* workspace, size_t workspace_bytes,

@@ -40,6 +40,11 @@ struct KPairParams {
     int pair_tiles;     // ceil(nwin / 2) * n_chunks
     int pair_windows;   // ceil(nwin / 2)
     int window_shift;   // peer output: the walk over the pair windows starts here (and wraps)
+    int chunk_group;    // 0: tiles walk all weight chunks of one pair window, then the next window;
+                        // g > 0: groups of g chunks outermost, pair windows inside, the g chunks innermost
+    unsigned int* wave_counter;   // NULL, or one zeroed counter per wave of tiles: the producers of all
+                                  // CTAs start a wave together (a bounded wait, given up silently)
+    int wave_slots;
 };
 
 template <bool kBf16, bool kPeer>
@@ -103,8 +108,21 @@ gemm_k_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     // Peer output: rank r starts its walk at the windows owned by rank r + 1, so that at any
     // moment the ranks store into different owners instead of all into the same one.
     auto decode = [&](int tile, int& pw, int& nchunk) {
-        pw = tile / p.n_chunks;
-        nchunk = tile - pw * p.n_chunks;
+        if (pp.chunk_group > 0) {
+            const int g = pp.chunk_group, per = pp.pair_windows * g, full = p.n_chunks / g;
+            if (tile < full * per) {
+                const int cg = tile / per, rem = tile - cg * per;
+                pw = rem / g;
+                nchunk = cg * g + rem - pw * g;
+            } else {                                   // the last, narrower group of chunks
+                const int rem = tile - full * per, wl = p.n_chunks - full * g;
+                pw = rem / wl;
+                nchunk = full * g + rem - pw * wl;
+            }
+        } else {
+            pw = tile / p.n_chunks;
+            nchunk = tile - pw * p.n_chunks;
+        }
         if constexpr (kPeer) {
             pw += pp.window_shift;
             if (pw >= pp.pair_windows) pw -= pp.pair_windows;
@@ -216,9 +234,30 @@ gemm_k_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
+            unsigned int* wave_counter = pp.wave_counter;
             for (int tile = pair; ok && tile < pp.pair_tiles; tile += npairs) {
                 int pw, nchunk;
                 decode(tile, pw, nchunk);
+                if (wave_counter) {
+                    // Tiles that share an operand find it in L2 only while their CTAs walk K at the
+                    // same time, and over tens of waves the CTAs drift apart (measured at 16384
+                    // tokens, K = 28672: 24.2 GB of DRAM reads per launch; with the producers lined
+                    // up at the start of every wave 7.9 GB).  Purely a hint: a producer that has
+                    // waited ~50 us (CTAs of this grid not resident, another launch using the same
+                    // counters) goes on alone and does not wait again.
+                    const int wv = (tile - pair) / npairs;
+                    if (wv > 0 && wv < pp.wave_slots) {
+                        atomicAdd(&wave_counter[wv], 1u);
+                        const long long t0 = clock64();
+                        while (*reinterpret_cast<volatile unsigned int*>(&wave_counter[wv]) < gridDim.x) {
+                            if (clock64() - t0 > 100000ll) {
+                                wave_counter = nullptr;
+                                break;
+                            }
+                            __nanosleep(200);
+                        }
+                    }
+                }
                 const int a_row = static_cast<int>((2ll * pw + rank) * kBM);
                 const int w_row = nchunk * 256 + rank * 128;
                 for (int w = 0; ok && w < p.words; ++w) {
@@ -351,6 +390,13 @@ gemm_k_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
 }
 
+// 1: groups of 8 weight chunks outermost and the producers of all CTAs lined up at every wave of
+// tiles (the default); 0: all chunks of one pair window, then the next window, no alignment
+int g_k_pair_wave_order = 1;
+constexpr int kWaveSlots = 1024;
+constexpr int kChunkGroup = 8;
+__device__ unsigned int g_k_pair_wave_counter[kWaveSlots];
+
 int gemm_k_pair_launch(const void* A, int64_t lda, const void* W, int64_t ldw, KParams p, int dtype,
                        cudaStream_t s)
 {
@@ -371,10 +417,34 @@ int gemm_k_pair_launch(const void* A, int64_t lda, const void* W, int64_t ldw, K
     pp.pair_windows = static_cast<int>((pp.nwin + 1) / 2);
     pp.pair_tiles = pp.pair_windows * pp.k.n_chunks;
     pp.window_shift = 0;
+    // A weight matrix that fits L2 is best left in the plain order (it stays resident while the
+    // activations stream through once; grouping the chunks would read the activations once per
+    // group instead).  Measured: N = 4096, K = 14336 (117 MB of weights, 8192 tokens) 0.80 ms plain
+    // against 0.86 ms grouped; N = 8192, K = 28672 (470 MB, 16384 tokens) 6.7 against 6.4 ms.
+    int l2_bytes = 0, dev = 0;
+    DPK_CUDA(cudaGetDevice(&dev));
+    DPK_CUDA(cudaDeviceGetAttribute(&l2_bytes, cudaDevAttrL2CacheSize, dev));
+    const bool grouped = g_k_pair_wave_order && 2.0 * p.N * p.K > 1.0 * l2_bytes;
+    pp.chunk_group = grouped ? kChunkGroup : 0;
+    pp.wave_counter = nullptr;
+    pp.wave_slots = 0;
     if (p.world > 1)
         pp.window_shift = static_cast<int>((int64_t((p.my_rank + 1) % p.world) * p.rows_per_owner / (2 * kBM)) %
                                            pp.pair_windows);
     if (2 * pp.pair_tiles < grid) grid = 2 * pp.pair_tiles;
+    if (grouped) {
+        // one counter per wave, zeroed on the stream ahead of the launch (the counters are one
+        // array per device: launches that overlap on two streams disturb each other's alignment,
+        // never their results)
+        const int waves = (pp.pair_tiles + grid / 2 - 1) / (grid / 2);
+        if (waves > 1 && waves <= kWaveSlots) {
+            void* ptr = nullptr;
+            DPK_CUDA(cudaGetSymbolAddress(&ptr, g_k_pair_wave_counter));
+            DPK_CUDA(cudaMemsetAsync(ptr, 0, sizeof(unsigned int) * waves, s));
+            pp.wave_counter = static_cast<unsigned int*>(ptr);
+            pp.wave_slots = waves;
+        }
+    }
     auto launch = [&](auto kernel, size_t smem_bytes) -> int {
         DPK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)smem_bytes));
@@ -396,3 +466,10 @@ int gemm_k_pair_launch(const void* A, int64_t lda, const void* W, int64_t ldw, K
 }
 
 }  // namespace dpk
+
+extern "C" int dpk_set_gemm_k_wave_order(int on)
+{
+    DPK_REQUIRE(on == 0 || on == 1, "on must be 0 or 1");
+    dpk::g_k_pair_wave_order = on;
+    return DPK_OK;
+}

@@ -36,6 +36,7 @@ SIGNATURES = {
                            _i32, _i32, _vp]),
     "dpk_set_gemm_mn_gather": (_i32, [_i32]),
     "dpk_set_router_norm_cluster": (_i32, [_i32]),
+    "dpk_set_gemm_k_wave_order": (_i32, [_i32]),
     "dpk_gemm_k": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32,
                           _vp, _i64, _vp, _sz, _vp]),
     "dpk_gemm_k_workspace_bytes": (_sz, [_i64, _i32]),

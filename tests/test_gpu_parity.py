@@ -1280,6 +1280,36 @@ def test_calls_are_cuda_graph_capturable(ops):
             torch.testing.assert_close(replayed.float(), out.float(), rtol=2 ** -6, atol=1e-3)
 
 
+def test_gemm_k_tile_orders_give_the_same_bits(ops):
+    """The CTA-pair kernel of the reduction-width projection walks its tiles in groups of weight
+    chunks with the producers lined up at every wave (default) or in the plain order: the order
+    only decides what is found in L2, every output element is summed the same way.  Several waves
+    of tiles, a ragged last window, a chunk count that is not a multiple of the group width."""
+    from dpk_b200 import _native
+    lib = _native.load()
+    bf = torch.bfloat16
+    g = seeded(11)
+    # the grouped order is taken where W exceeds L2 (126 MB): 147 MB here;
+    # 10 pair windows x 35 chunks = 350 pair tiles, the last group of chunks 3 wide
+    M, K, N, NG = 2500, 8192, 8960, 8
+    a = dev(bf16r(torch.randn(1, M, K, generator=g)), bf)
+    w = dev(bf16r(torch.randn(N, K, generator=g) * 0.02), bf)
+    res = dev(bf16r(torch.randn(1, M, N, generator=g)), bf)
+    mask = dev(torch.rand(1, M, NG, generator=g) > 0.4)
+    outs = []
+    try:
+        for on in (1, 0, 1):
+            _native.check(lib.dpk_set_gemm_k_wave_order(on))
+            outs.append(ops.gemm_k(a, w, mask, residual=res)[0].clone())
+    finally:
+        _native.check(lib.dpk_set_gemm_k_wave_order(1))
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    rows = torch.arange(0, M, 41)
+    want = O.gemm_k(a[:, rows].float().cpu(), w.float().cpu(), mask[:, rows].cpu()) + res[:, rows].float().cpu()
+    assert O.rel_err(outs[0][:, rows].float().cpu(), want) <= 2e-2
+    assert ops.device_status() == 0
+
+
 @pytest.mark.parametrize("H", [8192, 2080])
 def test_router_norm_is_cuda_graph_capturable(ops, H):
     """The router + norm call (a cluster launch at H = 8192, a plain launch at a width that does
