@@ -153,7 +153,10 @@ def run_ffn(args, decode=False):
 
 
 def run_gemm(args, which):
-    M, H, I, NG, keep = args.tokens or 8192, 4096, 14336, 112, 56
+    if args.config == 5:      # the FFN of the 70B-shaped layer
+        M, H, I, NG, keep = args.tokens or 16384, 8192, 28672, 224, 112
+    else:
+        M, H, I, NG, keep = args.tokens or 8192, 4096, 14336, 112, 56
     gen = torch.Generator(device="cuda").manual_seed(SEED)
     x, wg, wu, wd = _ffn_tensors(M, gen, H, I)
     mask = topk_mask((1, M, NG), keep, gen)
@@ -298,11 +301,16 @@ def main(argv=None):
                     help="gemm_mn / ffn: token rows by cp.async (0) or TMA tile::gather4 (1); -1 = the default")
     ap.add_argument("--heads-per-cta", type=int, default=0, choices=[0, 1, 2],
                     help="attention_prefill: 2 = the two-heads-per-CTA kernel, 0/1 = one head per CTA")
+    ap.add_argument("--config", type=int, default=2, choices=[2, 5],
+                    help="gemm_mn / gemm_k: FFN shape of BASELINE config 2 (4096/14336) or 5 (8192/28672)")
+    ap.add_argument("--wave-order", type=int, default=1, choices=[0, 1],
+                    help="gemm_k: 1 = grouped tile order with aligned waves where W exceeds L2, 0 = plain order")
     ap.add_argument("--router-cluster", type=int, default=1, choices=[0, 1],
                     help="router_norm: 1 = column-split cluster kernel where the width allows, 0 = one CTA per tile")
     args = ap.parse_args(argv)
     assert torch.cuda.is_available(), "dpk_b200.perf needs a CUDA device"
     _native.check(_native.load().dpk_set_router_norm_cluster(args.router_cluster))
+    _native.check(_native.load().dpk_set_gemm_k_wave_order(args.wave_order))
     _native.check(_native.load().dpk_set_attn_prefill_heads(args.heads_per_cta))
     if args.gather4 >= 0:
         _native.check(_native.load().dpk_set_gemm_mn_gather(args.gather4))
