@@ -865,6 +865,19 @@ def main():
                                   "under ncu, read from profiles/gemm_mn_pair_config5_counters.md (not "
                                   "measured by this run; null for other shapes)",
                 "algorithmic_flops_per_launch": flops_mn, "launch_ms": k_mn}
+    roof_down = None
+    if k_k and world == 1:
+        # the other large kernel: the down projection (reduction-width routed).  Rows of tokens that
+        # do not use a group still occupy MMA rows of their window's tile, so at a keep fraction f
+        # it executes 1/f times its algorithmic flops (every window visits every group here).
+        flops_k = 2.0 * H * 128 * nnz_f_local
+        executed = 2.0 * H * (shape.ffn_groups * 128.0) * T
+        roof_down = {"kernel": "gemm_k_pair_kernel (down projection + skip connection, CTA pairs)",
+                     "bound": "tensor", "achieved": flops_k / (k_k * 1e-3) / 1e12, "peak": sus,
+                     "unit": "TFLOP/s", "frac": flops_k / (k_k * 1e-3) / 1e12 / sus,
+                     "executed_tflops": executed / (k_k * 1e-3) / 1e12,
+                     "executed_frac": executed / (k_k * 1e-3) / 1e12 / sus,
+                     "algorithmic_flops_per_launch": flops_k, "launch_ms": k_k}
     cpu = None
     if not args.no_cpu_baseline and world == 1:
         R, secs = cpu_layer_leg(shape, 3, 1)
@@ -886,6 +899,7 @@ def main():
                            "frac": flops / (ms_step * 1e-3) / 1e12 / (sus * world),
                            "peak_source": f"{peak_src} sustained bf16 x {world} GPU(s)"},
         "roofline": roof,
+        "roofline_down_projection": roof_down,
         "kernels": {"gemm_mn_ms": k_mn, "gemm_k_ms": k_k,
                     "gemm_k_ms_covers": ("down projection + barriers + reduce/gather" if fused else "down projection"),
                     "phases_ms": phases},
