@@ -247,9 +247,12 @@ gemm_k_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     // counters) goes on alone and does not wait again.
                     const int wv = (tile - pair) / npairs;
                     if (wv > 0 && wv < pp.wave_slots) {
+                        // both CTAs of every pair that has a tile in this wave (the last wave is short)
+                        const int left = pp.pair_tiles - wv * npairs;
+                        const unsigned int expected = 2u * static_cast<unsigned int>(left < npairs ? left : npairs);
                         atomicAdd(&wave_counter[wv], 1u);
                         const long long t0 = clock64();
-                        while (*reinterpret_cast<volatile unsigned int*>(&wave_counter[wv]) < gridDim.x) {
+                        while (*reinterpret_cast<volatile unsigned int*>(&wave_counter[wv]) < expected) {
                             if (clock64() - t0 > 100000ll) {
                                 wave_counter = nullptr;
                                 break;
