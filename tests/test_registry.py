@@ -96,3 +96,15 @@ def test_install_into_reference_style_module():
     backend, target, kw = ref.seen["gemm_mn"]
     assert backend == "b200" and callable(target)
     assert kw["variants"] == {0: ("sm100",)} and kw["priority"] > 100
+
+
+def test_attention_head_sizes_the_operators_take():
+    """The kernels are built for head sizes 64 and 128; the operators also take the other
+    multiples of 32 up to 128 (the reference's rule is D % 32 == 0) by padding, and refuse
+    the rest with a message instead of a kernel error."""
+    from dpk_b200 import ops
+
+    assert [ops._padded_head_dim(d) for d in (32, 64, 96, 128)] == [64, 64, 128, 128]
+    for bad in (0, 48, 160, 256):
+        with pytest.raises(ValueError, match="head_dim"):
+            ops._padded_head_dim(bad)
